@@ -1,0 +1,287 @@
+// Host side of libflashfwd_b200.so: argument checks, TMA descriptors, kernel dispatch and the
+// status word. Declared in include/flash_forward_b200.h. This is the replacement for the
+// reference's run_flash_attention / run_kernel / create_tensor_map
+// (src/flash_forward.h:593-665, :369-590 and include/utils.h:168-186 of the reference):
+// same inputs, but asynchronous on a caller stream, on the current device, re-entrant
+// (descriptors are per-call kernel parameters, not globals), and with status codes in place
+// of exit/abort/throw.
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/flash_forward_b200.h"
+#include "fwd_params.h"
+#include "fwd_persistent.cuh"
+#include "fwd_serial.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, const char* a = "", const char* b = "") {
+  snprintf(g_err, sizeof(g_err), fmt, a, b);
+  return code;
+}
+int fail_cuda(const char* what, cudaError_t e) {
+  snprintf(g_err, sizeof(g_err), "%s: %s", what, cudaGetErrorString(e));
+  return FA_CUDA_ERROR;
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is looked up at run time so that the library links against the CUDA
+// runtime only and can be loaded (for symbol checks) on a machine without a driver.
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+constexpr int kMaxDevices = 64;
+struct DeviceState {
+  std::mutex mu;
+  bool probed = false;
+  bool is_sm100 = false;
+  int num_sms = 0;
+  int* status = nullptr;  // device word
+  bool attr_set[8] = {};
+};
+DeviceState g_dev[kMaxDevices];
+
+int device_state(DeviceState** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail_cuda("cudaGetDevice", e);
+  if (dev < 0 || dev >= kMaxDevices) return fail(FA_UNSUPPORTED, "device ordinal out of range");
+  DeviceState& s = g_dev[dev];
+  std::lock_guard<std::mutex> lk(s.mu);
+  if (!s.probed) {
+    int major = 0, sms = 0;
+    if ((e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess)
+      return fail_cuda("cudaDeviceGetAttribute", e);
+    if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess)
+      return fail_cuda("cudaDeviceGetAttribute", e);
+    s.is_sm100 = (major == 10);
+    s.num_sms = sms;
+    if (s.is_sm100) {
+      if ((e = cudaMalloc(&s.status, sizeof(int))) != cudaSuccess) return fail_cuda("cudaMalloc(status)", e);
+      if ((e = cudaMemset(s.status, 0, sizeof(int))) != cudaSuccess) return fail_cuda("cudaMemset(status)", e);
+    }
+    s.probed = true;
+  }
+  *out = &s;
+  return FA_OK;
+}
+
+// 4-D map over one [bh][seqlen][head_dim] fp16 tensor: {64 contiguous elements, row, 64-wide
+// panel, head}. One box = 128 rows x all panels of one head, landing in shared memory as
+// [panel][row][64] with the 128-byte swizzle a UMMA descriptor expects. Out-of-range rows of
+// a ragged last tile read as zero.
+int make_map(CUtensorMap* map, const void* base, int bh, int seqlen, int head_dim, int box_rows) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return fail(FA_CUDA_ERROR, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t dims[4] = {64, (cuuint64_t)seqlen, (cuuint64_t)(head_dim / 64), (cuuint64_t)bh};
+  cuuint64_t strides[3] = {(cuuint64_t)head_dim * 2, 128, (cuuint64_t)seqlen * head_dim * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, (cuuint32_t)(head_dim / 64), 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_err, sizeof(g_err), "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return FA_CUDA_ERROR;
+  }
+  return FA_OK;
+}
+
+template <typename K>
+int ensure_smem_attr(DeviceState* s, int slot, K kernel, int bytes) {
+  std::lock_guard<std::mutex> lk(s->mu);
+  if (s->attr_set[slot]) return FA_OK;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(MaxDynamicSharedMemorySize)", e);
+  s->attr_set[slot] = true;
+  return FA_OK;
+}
+
+template <int D>
+int launch_serial(DeviceState* s, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                  const fa::FwdParams& p, cudaStream_t st) {
+  using Cfg = fa::SerialCfg<D>;
+  int rc = ensure_smem_attr(s, D == 64 ? 0 : 1, fa::fwd_serial_kernel<D>, Cfg::kSmemBytes);
+  if (rc != FA_OK) return rc;
+  dim3 grid((p.seqlen + fa::kBlockM - 1) / fa::kBlockM, p.bh);
+  fa::fwd_serial_kernel<D><<<grid, 128, Cfg::kSmemBytes, st>>>(mq, mk, mv, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail_cuda("launch fwd_serial_kernel", e);
+  return FA_OK;
+}
+
+template <int D>
+int launch_persistent(DeviceState* s, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                      const fa::FwdParams& p, cudaStream_t st) {
+  using Cfg = fa::PersistentCfg<D>;
+  int rc = ensure_smem_attr(s, D == 64 ? 2 : 3, fa::fwd_persistent_kernel<D>, Cfg::kSmemBytes);
+  if (rc != FA_OK) return rc;
+  int grid = p.num_items < s->num_sms ? p.num_items : s->num_sms;
+  fa::fwd_persistent_kernel<D><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mk, mv, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail_cuda("launch fwd_persistent_kernel", e);
+  return FA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* flash_forward_last_error(void) { return g_err; }
+
+double flash_forward_flops(int batch, int heads, int seqlen, int head_dim, int is_causal, int window_left,
+                           int window_right) {
+  const double bh = (double)batch * heads, n = seqlen, d = head_dim;
+  const int wr = fa::eff_window_right(is_causal, window_right);
+  if (window_left < 0 && window_right < 0) return (is_causal ? 2.0 : 4.0) * bh * n * n * d;
+  double pairs = 0;  // exact count of visible (query, key) pairs of one head
+  for (int i = 0; i < seqlen; ++i) {
+    int lo = window_left >= 0 ? i - window_left : 0;
+    int hi = wr >= 0 ? i + wr : seqlen - 1;
+    if (lo < 0) lo = 0;
+    if (hi > seqlen - 1) hi = seqlen - 1;
+    if (hi >= lo) pairs += hi - lo + 1;
+  }
+  return 4.0 * bh * pairs * d;
+}
+
+int flash_forward_ex(const void* q, const void* k, const void* v, void* o, int batch, int heads, int seqlen,
+                     int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,
+                     void* stream, int kernel, int variant, float* dbg) {
+  if (!q || !k || !v || !o) return fail(FA_INVALID_ARG, "null tensor pointer");
+  if (batch <= 0 || heads <= 0 || seqlen <= 0) return fail(FA_INVALID_ARG, "batch, heads and seqlen must be positive");
+  if (head_dim != 64 && head_dim != 128) return fail(FA_UNSUPPORTED, "head_dim must be 64 or 128");
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(o)) & 15)
+    return fail(FA_INVALID_ARG, "tensor pointers must be 16-byte aligned");
+  if ((long long)batch * heads > 0x7fffffffLL) return fail(FA_INVALID_ARG, "batch*heads overflows int");
+  if (kernel < 0 || kernel > 1) return fail(FA_INVALID_ARG, "kernel must be 0 (persistent) or 1 (serial)");
+  if (!(softmax_scale == softmax_scale)) return fail(FA_INVALID_ARG, "softmax_scale is NaN");
+
+  DeviceState* s = nullptr;
+  int rc = device_state(&s);
+  if (rc != FA_OK) return rc;
+  if (!s->is_sm100) return fail(FA_UNSUPPORTED, "this library runs on compute capability 10.x (B200) only");
+
+  const int bh = batch * heads;
+  if (softmax_scale <= 0.f) softmax_scale = 1.0f / sqrtf((float)head_dim);
+
+  fa::FwdParams p;
+  memset(&p, 0, sizeof(p));
+  p.O = static_cast<__half*>(o);
+  p.seqlen = seqlen;
+  p.bh = bh;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.causal = is_causal ? 1 : 0;
+  p.window_left = window_left < 0 ? -1 : window_left;
+  p.window_right = window_right < 0 ? -1 : window_right;
+  p.status = s->status;
+  p.dbg = dbg;
+  p.variant = variant;
+  p.num_q_pairs = (seqlen + 2 * fa::kBlockM - 1) / (2 * fa::kBlockM);
+  if ((long long)bh * p.num_q_pairs > 0x7fffffffLL) return fail(FA_INVALID_ARG, "too many work items");
+  p.num_items = bh * p.num_q_pairs;
+
+  CUtensorMap mq, mk, mv;
+  if ((rc = make_map(&mq, q, bh, seqlen, head_dim, fa::kBlockM)) != FA_OK) return rc;
+  if ((rc = make_map(&mk, k, bh, seqlen, head_dim, fa::kBlockN)) != FA_OK) return rc;
+  if ((rc = make_map(&mv, v, bh, seqlen, head_dim, fa::kBlockN)) != FA_OK) return rc;
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (kernel == 1) {
+    return head_dim == 64 ? launch_serial<64>(s, mq, mk, mv, p, st) : launch_serial<128>(s, mq, mk, mv, p, st);
+  }
+  return head_dim == 64 ? launch_persistent<64>(s, mq, mk, mv, p, st) : launch_persistent<128>(s, mq, mk, mv, p, st);
+}
+
+int flash_forward(const void* q, const void* k, const void* v, void* o, int batch, int heads, int seqlen,
+                  int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,
+                  void* stream) {
+  return flash_forward_ex(q, k, v, o, batch, heads, seqlen, head_dim, softmax_scale, is_causal, window_left,
+                          window_right, stream, 0, 0, nullptr);
+}
+
+int flash_forward_check(void* stream) {
+  DeviceState* s = nullptr;
+  int rc = device_state(&s);
+  if (rc != FA_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return fail_cuda("cudaStreamSynchronize", e);
+  if (!s->status) return FA_OK;
+  int host = 0;
+  if ((e = cudaMemcpy(&host, s->status, sizeof(int), cudaMemcpyDeviceToHost)) != cudaSuccess)
+    return fail_cuda("cudaMemcpy(status)", e);
+  if (host != 0) {
+    cudaMemset(s->status, 0, sizeof(int));
+    snprintf(g_err, sizeof(g_err), "a wait inside the attention kernel ran out of time (status word %d)", host);
+    return FA_DEVICE_TIMEOUT;
+  }
+  return FA_OK;
+}
+
+int run_flash_attention_c(int B, int N, int S, int d, void* Q, void* K, void* V, void* O, void* L, void* M,
+                          int Is_dropout, int Is_causal, int Is_local, int Has_alibi, int window_size,
+                          float* alibi_slopes, float dropout_prob, void* states) {
+  (void)L; (void)M; (void)alibi_slopes; (void)dropout_prob; (void)states;
+  if (Is_dropout) return fail(FA_UNSUPPORTED, "dropout is outside this library's path");
+  if (Has_alibi) return fail(FA_UNSUPPORTED, "ALiBi is outside this library's path");
+  if (Is_local && window_size < 0) return fail(FA_INVALID_ARG, "Is_local needs window_size >= 0");
+  const int wl = Is_local ? window_size : -1;
+  const int wr = Is_local ? window_size : -1;
+  cudaEvent_t t0, t1;
+  cudaError_t e;
+  if ((e = cudaEventCreate(&t0)) != cudaSuccess) return fail_cuda("cudaEventCreate", e);
+  if ((e = cudaEventCreate(&t1)) != cudaSuccess) { cudaEventDestroy(t0); return fail_cuda("cudaEventCreate", e); }
+  cudaEventRecord(t0, 0);
+  int rc = flash_forward(Q, K, V, O, B, N, S, d, 0.f, Is_causal, wl, wr, nullptr);
+  cudaEventRecord(t1, 0);
+  if (rc == FA_OK) rc = flash_forward_check(nullptr);
+  float ms = 0.f;
+  if (rc == FA_OK && cudaEventSynchronize(t1) == cudaSuccess && cudaEventElapsedTime(&ms, t0, t1) == cudaSuccess)
+    printf("TIME: %f\n", ms);
+  cudaEventDestroy(t0);
+  cudaEventDestroy(t1);
+  return rc;
+}
+
+int flash_forward_shutdown(void) {
+  int prev = 0;
+  if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+  for (int d = 0; d < kMaxDevices; ++d) {
+    DeviceState& s = g_dev[d];
+    std::lock_guard<std::mutex> lk(s.mu);
+    if (s.status) {
+      cudaSetDevice(d);
+      cudaFree(s.status);
+      s.status = nullptr;
+    }
+    s.probed = false;
+    for (bool& b : s.attr_set) b = false;
+  }
+  if (prev >= 0) cudaSetDevice(prev);
+  return FA_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,92 @@
+/* C ABI of the B200 (sm_100a) attention-forward library, libflashfwd_b200.so.
+ *
+ * Plain pointers and sizes only: no C++ types, no torch types. All tensor pointers are device
+ * pointers on the calling thread's current CUDA device. Layout of Q, K, V, O: fp16, contiguous
+ * [batch][heads][seqlen][head_dim] with head_dim fastest, the layout the reference's host entry
+ * point takes (src/main.cu:173,182 and src/flash_forward.h:378 of the reference).
+ *
+ * Every function returns an FA_* status code; none of them exits, aborts or throws (the
+ * reference does all three: include/utils.h:16-23, src/flash_forward.h:384-387, :588).
+ */
+#ifndef FLASH_FORWARD_B200_H
+#define FLASH_FORWARD_B200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  FA_OK = 0,
+  FA_INVALID_ARG = 1,    /* null or misaligned pointer, non-positive size */
+  FA_UNSUPPORTED = 2,    /* head_dim not 64/128, dropout, ALiBi, device is not sm_100 */
+  FA_CUDA_ERROR = 3,     /* a CUDA runtime/driver call failed; see flash_forward_last_error() */
+  FA_DEVICE_TIMEOUT = 4  /* a bounded wait inside the kernel gave up (status word set) */
+};
+
+/* Attention forward O = softmax(scale * Q K^T + mask) V, asynchronous on `stream`.
+ *
+ * Replaces the launch path of the reference: run_flash_attention (src/flash_forward.h:593-665)
+ * -> run_kernel (src/flash_forward.h:369-590) -> forward_kernel (src/flash_forward.h:78-366),
+ * with the argument list the reference's call site uses (src/main.cu:99) reduced to what the
+ * path reads: Q/K/V/O, batch, heads, seqlen, head_dim, softmax scale, causal flag, window.
+ *
+ *   softmax_scale <= 0  -> 1/sqrt(head_dim)  (what the reference hard-codes, :639)
+ *   is_causal != 0      -> key j visible to query i only if j <= i
+ *   window_left  >= 0   -> key j visible only if j >= i - window_left   (< 0: unbounded)
+ *   window_right >= 0   -> key j visible only if j <= i + window_right  (< 0: unbounded)
+ *   stream              -> a cudaStream_t passed as void* (NULL = default stream)
+ *
+ * head_dim must be 64 or 128 (reference: src/flash_forward.h:588). seqlen may be any positive
+ * value (the reference silently requires a multiple of 128). Pointers must be 16-byte aligned.
+ * The call returns once the kernel is enqueued; use flash_forward_check() to learn whether a
+ * device-side wait timed out.
+ */
+int flash_forward(const void* q, const void* k, const void* v, void* o, int batch, int heads, int seqlen,
+                  int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,
+                  void* stream);
+
+/* Same operation with an explicit kernel choice, for tests and bring-up:
+ *   kernel  0 = default (warp-specialised persistent kernel), 1 = serial one-tile-per-CTA kernel
+ *   variant kernel-specific switches (serial kernel: bit0 stages P in shared memory)
+ *   dbg     optional device buffer of 128*128 + 128*head_dim floats receiving the raw first
+ *           score tile and first P.V product of q tile 0 / head 0 (serial kernel), else NULL
+ * No counterpart in the reference (it has a single kernel).
+ */
+int flash_forward_ex(const void* q, const void* k, const void* v, void* o, int batch, int heads, int seqlen,
+                     int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,
+                     void* stream, int kernel, int variant, float* dbg);
+
+/* Waits for `stream`, then reads and clears the current device's status word. Returns FA_OK,
+ * FA_DEVICE_TIMEOUT, or FA_CUDA_ERROR. Replaces the reference's CUDA_CHECK(cudaDeviceSynchronize())
+ * + exit (src/flash_forward.h:654-655). */
+int flash_forward_check(void* stream);
+
+/* The reference's host entry point, positional argument for positional argument
+ * (src/flash_forward.h:593-612; `N` is the number of heads and `S` the sequence length there).
+ * Blocking, prints "TIME: <ms>" like src/flash_forward.h:664. Mapping:
+ *   Is_local  -> window_left = window_right = window_size (symmetric, :640-641; mask.h:55)
+ *   Is_causal -> window_right = 0 (both masks apply when both flags are set, mask.h:15,:43)
+ *   L, M      -> ignored (the reference never reads them)
+ *   Is_dropout / Has_alibi -> FA_UNSUPPORTED (outside this library's path)
+ * Unlike the reference it runs on the current device and returns a status instead of exiting. */
+int run_flash_attention_c(int B, int N, int S, int d, void* Q, void* K, void* V, void* O, void* L, void* M,
+                          int Is_dropout, int Is_causal, int Is_local, int Has_alibi, int window_size,
+                          float* alibi_slopes, float dropout_prob, void* states);
+
+/* Message for the last non-OK status returned on the calling thread ("" if none). */
+const char* flash_forward_last_error(void);
+
+/* Algorithmic work of one call: FLOPs = 4 * (visible query-key pairs) * head_dim summed over
+ * batch*heads, the count the throughput figures use (4*B*H*N^2*d dense, halved for causal). */
+double flash_forward_flops(int batch, int heads, int seqlen, int head_dim, int is_causal, int window_left,
+                           int window_right);
+
+/* Frees the per-device status words this library allocated. Optional. */
+int flash_forward_shutdown(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASH_FORWARD_B200_H */
