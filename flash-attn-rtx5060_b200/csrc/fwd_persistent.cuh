@@ -1,9 +1,443 @@
+// Warp-specialised persistent attention-forward kernel for sm_100a.
+//
+// One CTA per SM walks a list of work items; a work item is a pair of adjacent 128-row q tiles
+// of one (batch, head). Roles (16 warps):
+//   warps 0-3   softmax of q tile 0: one thread per score row (TMEM lane), exp2 online softmax
+//   warps 4-7   softmax of q tile 1
+//   warps 8-11  correction: rescales the running output in TMEM when a row max moved, and the
+//               epilogue (O / l -> fp16 -> global)
+//   warp 12     tensor-core issuer: one thread issues every tcgen05.mma
+//   warp 13     TMA producer: Q tiles and the K/V tile ring
+//   warps 14-15 idle (they only donate registers)
+// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D); the fp16 P tile of a
+// stage overwrites the first 64 columns of its own S.
+//
+// Replaces the reference's forward_kernel, Schedule and SMem (src/flash_forward.h:22-366),
+// apply_mask (src/mask.h:10-84) and apply_softmax (src/softmax.h:9-86): same function, but
+// the contractions run on tcgen05 with TMEM accumulators, the two q tiles ping-pong so that
+// the tensor pipe works on one while the other is in softmax, masks touch only boundary
+// tiles, kv tiles outside a q tile's visible range are never loaded for it, and the output
+// is rescaled lazily.
 #pragma once
 #include "fwd_params.h"
 #include "ptx.cuh"
+
+#ifndef FA_REG_SOFTMAX
+#define FA_REG_SOFTMAX 176
+#define FA_REG_CORR 96
+#define FA_REG_MISC 64
+#endif
+
 namespace fa {
-template <int D> struct PersistentCfg { static constexpr int kThreads = 512; static constexpr int kSmemBytes = 1024; };
+
 template <int D>
-__global__ void fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
-                  const __grid_constant__ CUtensorMap mapV, const FwdParams p) { if (threadIdx.x==0 && blockIdx.x==0) atomicExch(p.status, 99); }
+struct PersistentCfg {
+  static constexpr int kThreads = 512;
+  static constexpr int kTileBytes = kBlockN * D * 2;
+  static constexpr int kPanelBytes = kBlockN * kPanel * 2;
+  static constexpr int kStages = (D == 128) ? 5 : 8;  // ring slots, each one K or one V tile
+  static constexpr int kOffQ = 0;
+  static constexpr int kOffKV = 2 * kTileBytes;
+  static constexpr int kOffAlpha = kOffKV + kStages * kTileBytes;  // float[2][128]
+  static constexpr int kOffRowSum = kOffAlpha + 2 * kBlockM * 4;   // float[2][128]
+  static constexpr int kOffBars = kOffRowSum + 2 * kBlockM * 4;
+  static constexpr int kNumBars = 14 + 2 * kStages;
+  static constexpr int kOffMisc = kOffBars + kNumBars * 8;
+  static constexpr int kSmemBytes = kOffMisc + 16;
+  static constexpr uint32_t kTmemCols = 512;
+  static constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
+  // softmax threshold (in log2 units) below which a larger row max does not trigger a rescale
+  static constexpr float kLazyLog2 = 8.f;
+};
+
+// Work item -> geometry. Every role decodes the same item the same way.
+struct ItemGeom {
+  int bh, pair;
+  int r0[2], r1[2];  // first / last q row of each stage's tile (r1 < r0: stage has no rows)
+  int lo[2], hi[2];  // visible kv-tile range of each stage, [lo, hi); empty when no rows
+  int lo_all, hi_all;
+};
+
+// Items are ordered head-major with the longest (latest) q pair of each head first, so that a
+// causal launch starts with the most expensive items and CTAs that run together share K/V in L2.
+__device__ __forceinline__ ItemGeom decode_item(int item, const FwdParams& p) {
+  ItemGeom g;
+  g.bh = item / p.num_q_pairs;
+  g.pair = p.num_q_pairs - 1 - (item - g.bh * p.num_q_pairs);
+  const int wr = eff_window_right(p.causal, p.window_right);
+  g.lo_all = 0x7fffffff;
+  g.hi_all = 0;
+#pragma unroll
+  for (int s = 0; s < 2; ++s) {
+    g.r0[s] = g.pair * 2 * kBlockM + s * kBlockM;
+    if (g.r0[s] >= p.seqlen) {
+      g.r1[s] = g.r0[s] - 1;
+      g.lo[s] = g.hi[s] = 0;
+    } else {
+      g.r1[s] = min(g.r0[s] + kBlockM, p.seqlen) - 1;
+      g.lo[s] = kv_tile_begin(g.r0[s], p.window_left);
+      g.hi[s] = kv_tile_end(g.r1[s], wr, p.seqlen);
+      g.lo_all = min(g.lo_all, g.lo[s]);
+      g.hi_all = max(g.hi_all, g.hi[s]);
+    }
+  }
+  return g;
 }
+
+template <int D>
+__global__ void __launch_bounds__(512, 1)
+fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                      const __grid_constant__ CUtensorMap mapV, const FwdParams p) {
+  using Cfg = PersistentCfg<D>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  if ((smem_u32(smem) & 1023u) != 0) {  // swizzled tiles need a 1024-byte aligned base
+    if (tid == 0) atomicExch(p.status, 2);
+    return;
+  }
+
+  uint8_t* sQ = smem + Cfg::kOffQ;
+  uint8_t* sKV = smem + Cfg::kOffKV;
+  float* sAlpha = reinterpret_cast<float*>(smem + Cfg::kOffAlpha);
+  float* sRowSum = reinterpret_cast<float*>(smem + Cfg::kOffRowSum);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBars);
+  uint64_t* q_full = bars;            // [2] TMA -> MMA
+  uint64_t* q_empty = bars + 2;       // [2] MMA -> TMA
+  uint64_t* s_full = bars + 4;        // [2] MMA -> softmax: S tile in TMEM
+  uint64_t* p_full = bars + 6;        // [2] softmax (P written) + correction (O rescaled) -> MMA
+  uint64_t* alpha_ready = bars + 8;   // [2] softmax -> correction: rescale factors in smem
+  uint64_t* l_ready = bars + 10;      // [2] softmax -> correction: final row sums in smem
+  uint64_t* o_full = bars + 12;       // [2] MMA -> correction: last P.V of the item landed
+  uint64_t* kv_full = bars + 14;      // [kStages] TMA -> MMA
+  uint64_t* kv_empty = bars + 14 + Cfg::kStages;  // [kStages] MMA -> TMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::kOffMisc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  if (warp == 12) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 1);
+      mbar_init(&s_full[s], 1);
+      mbar_init(&p_full[s], 8);  // one arrival per softmax warp and per correction warp
+      mbar_init(&alpha_ready[s], 4);
+      mbar_init(&l_ready[s], 4);
+      mbar_init(&o_full[s], 1);
+    }
+    for (int i = 0; i < Cfg::kStages; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 13 && lane == 0) {
+    prefetch_tensormap(&mapQ);
+    prefetch_tensormap(&mapK);
+    prefetch_tensormap(&mapV);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int N = p.seqlen;
+  const int wl = p.window_left;
+  const int wr = eff_window_right(p.causal, p.window_right);
+
+  if (warp < 8) {
+    // =====================================================================================
+    // softmax: stage s = warp / 4, row = tid % 128
+    // =====================================================================================
+    reg_inc<FA_REG_SOFTMAX>();
+    const int s = warp >> 2;
+    const int row_l = tid & 127;
+    const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32u;
+    const uint32_t tS = tmem_addr(tmem_base, lane_base, s == 0 ? Cfg::kColS0 : Cfg::kColS1);
+    uint32_t n_s = 0;  // completed s_full phases
+    bool ok = true;
+    for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
+      const ItemGeom g = decode_item(item, p);
+      const int q_r0 = s ? g.r0[1] : g.r0[0];
+      const int q_r1 = s ? g.r1[1] : g.r1[0];
+      const int j_lo = s ? g.lo[1] : g.lo[0];
+      const int j_hi = s ? g.hi[1] : g.hi[0];
+      if (q_r1 < q_r0) continue;
+      const int row = q_r0 + row_l;
+      float m_run = -INFINITY;  // true running max of the raw scores
+      float m_used = 0.f;       // max the exponentials are currently taken against
+      float l_run = 0.f;
+      for (int j = j_lo; j < j_hi; ++j) {
+        if (!mbar_wait_warp(&s_full[s], n_s & 1, abort_flag)) { ok = false; break; }
+        ++n_s;
+        tc_fence_after();
+        uint32_t r0[32], r1[32], r2[32], r3[32];
+        tmem_ld32(tS + 0, r0);
+        tmem_ld32(tS + 32, r1);
+        tmem_ld32(tS + 64, r2);
+        tmem_ld32(tS + 96, r3);
+        tmem_wait_ld();
+        tmem_ld_fence(r0);
+        tmem_ld_fence(r1);
+        tmem_ld_fence(r2);
+        tmem_ld_fence(r3);
+        float sc[kBlockN];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          sc[i] = __uint_as_float(r0[i]);
+          sc[32 + i] = __uint_as_float(r1[i]);
+          sc[64 + i] = __uint_as_float(r2[i]);
+          sc[96 + i] = __uint_as_float(r3[i]);
+        }
+        const int kv0 = j * kBlockN;
+        if (kv_tile_needs_mask(kv0, q_r0, q_r1, wl, wr, N)) {
+          const int c_lo = (wl >= 0) ? row - wl - kv0 : -1;
+          int c_hi = N - 1 - kv0;
+          if (wr >= 0) c_hi = min(c_hi, row + wr - kv0);
+#pragma unroll
+          for (int c = 0; c < kBlockN; ++c)
+            if (c < c_lo || c > c_hi) sc[c] = -INFINITY;
+        }
+        float mx0 = sc[0], mx1 = sc[1], mx2 = sc[2], mx3 = sc[3];
+#pragma unroll
+        for (int c = 4; c < kBlockN; c += 4) {
+          mx0 = fmaxf(mx0, sc[c]);
+          mx1 = fmaxf(mx1, sc[c + 1]);
+          mx2 = fmaxf(mx2, sc[c + 2]);
+          mx3 = fmaxf(mx3, sc[c + 3]);
+        }
+        const float m_new = fmaxf(fmaxf(m_run, fmaxf(mx0, mx1)), fmaxf(mx2, mx3));
+        // Lazy rescale: keep the old reference max unless the true max moved by more than
+        // kLazyLog2 (P then stays below 2^8, well inside fp16), or no finite score was seen yet.
+        float alpha = 1.f;
+        if (m_run == -INFINITY) {
+          m_used = (m_new == -INFINITY) ? 0.f : m_new;
+        } else if ((m_new - m_used) * p.scale_log2 > Cfg::kLazyLog2) {
+          alpha = ex2_approx((m_used - m_new) * p.scale_log2);
+          m_used = m_new;
+        }
+        m_run = m_new;
+        sAlpha[s * kBlockM + row_l] = alpha;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&alpha_ready[s]);
+
+        const float neg_ms = -m_used * p.scale_log2;
+        float l0 = 0.f, l1 = 0.f;
+        uint32_t pk0[32], pk1[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const float e0 = ex2_approx(fmaf(sc[2 * c], p.scale_log2, neg_ms));
+          const float e1 = ex2_approx(fmaf(sc[2 * c + 1], p.scale_log2, neg_ms));
+          l0 += e0;
+          l1 += e1;
+          pk0[c] = pack_f16x2(e0, e1);
+        }
+        tmem_st32(tS + 0, pk0);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const float e0 = ex2_approx(fmaf(sc[64 + 2 * c], p.scale_log2, neg_ms));
+          const float e1 = ex2_approx(fmaf(sc[64 + 2 * c + 1], p.scale_log2, neg_ms));
+          l0 += e0;
+          l1 += e1;
+          pk1[c] = pack_f16x2(e0, e1);
+        }
+        tmem_st32(tS + 32, pk1);
+        l_run = l_run * alpha + (l0 + l1);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[s]);
+      }
+      if (!ok) break;
+      sRowSum[s * kBlockM + row_l] = l_run;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&l_ready[s]);
+    }
+  } else if (warp < 12) {
+    // =====================================================================================
+    // correction + epilogue: row = tid % 128 of both stages
+    // =====================================================================================
+    reg_dec<FA_REG_CORR>();
+    const int row_l = tid & 127;
+    const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32u;
+    uint32_t n_alpha[2] = {0, 0}, n_l[2] = {0, 0}, n_o[2] = {0, 0};
+    bool ok = true;
+    for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
+      const ItemGeom g = decode_item(item, p);
+      for (int j = g.lo_all; j < g.hi_all && ok; ++j) {
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          if (j < g.lo[s] || j >= g.hi[s]) continue;
+          if (!mbar_wait_warp(&alpha_ready[s], n_alpha[s] & 1, abort_flag)) { ok = false; break; }
+          ++n_alpha[s];
+          const float alpha = sAlpha[s * kBlockM + row_l];
+          if (j > g.lo[s] && __any_sync(0xffffffffu, alpha != 1.f)) {
+            tc_fence_after();
+            const uint32_t tO = tmem_addr(tmem_base, lane_base, s == 0 ? Cfg::kColO0 : Cfg::kColO1);
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t r[32];
+              tmem_ld32(tO + c * 32, r);
+              tmem_wait_ld();
+              tmem_ld_fence(r);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+              tmem_st32(tO + c * 32, r);
+            }
+            tmem_wait_st();
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&p_full[s]);
+        }
+      }
+      if (!ok) break;
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        if (g.r1[s] < g.r0[s]) continue;
+        if (!mbar_wait_warp(&l_ready[s], n_l[s] & 1, abort_flag)) { ok = false; break; }
+        ++n_l[s];
+        const float l = sRowSum[s * kBlockM + row_l];
+        if (!mbar_wait_warp(&o_full[s], n_o[s] & 1, abort_flag)) { ok = false; break; }
+        ++n_o[s];
+        tc_fence_after();
+        const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+        const int row = g.r0[s] + row_l;
+        const uint32_t tO = tmem_addr(tmem_base, lane_base, s == 0 ? Cfg::kColO0 : Cfg::kColO1);
+        __half* orow = p.O + (static_cast<size_t>(g.bh) * N + row) * D;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tO + c * 32, r);
+          tmem_wait_ld();
+          tmem_ld_fence(r);
+          if (row < N) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 v;
+              v.x = pack_f16x2(__uint_as_float(r[i * 8 + 0]) * inv_l, __uint_as_float(r[i * 8 + 1]) * inv_l);
+              v.y = pack_f16x2(__uint_as_float(r[i * 8 + 2]) * inv_l, __uint_as_float(r[i * 8 + 3]) * inv_l);
+              v.z = pack_f16x2(__uint_as_float(r[i * 8 + 4]) * inv_l, __uint_as_float(r[i * 8 + 5]) * inv_l);
+              v.w = pack_f16x2(__uint_as_float(r[i * 8 + 6]) * inv_l, __uint_as_float(r[i * 8 + 7]) * inv_l);
+              *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = v;
+            }
+          }
+        }
+      }
+    }
+  } else {
+    reg_dec<FA_REG_MISC>();
+    if (warp == 12 && lane == 0) {
+      // ===================================================================================
+      // tensor-core issuer
+      // ===================================================================================
+      constexpr uint32_t idesc_qk = umma_idesc_f16(kBlockM, kBlockN, 0, 0);
+      constexpr uint32_t idesc_pv = umma_idesc_f16(kBlockM, D, 0, 1);
+      const uint32_t q_addr = smem_u32(sQ);
+      const uint32_t kv_addr = smem_u32(sKV);
+      uint32_t it_base = 0;  // ring position of K tile lo_all of the current item
+      uint32_t n_p[2] = {0, 0}, n_q[2] = {0, 0};
+      bool ok = true;
+      for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
+        const ItemGeom g = decode_item(item, p);
+        for (int j = g.lo_all - 1; j < g.hi_all && ok; ++j) {
+#pragma unroll
+          for (int s = 0; s < 2; ++s) {
+            const bool act_j = (j >= g.lo[s] && j < g.hi[s]);
+            const bool act_n = (j + 1 >= g.lo[s] && j + 1 < g.hi[s]);
+            const bool other_j = (s == 0) && (j >= g.lo[1] && j < g.hi[1]);          // stage 1 still needs V_j
+            const bool other_n = (s == 0) && (j + 1 >= g.lo[1] && j + 1 < g.hi[1]);  // stage 1 still needs K_j+1
+            const uint32_t colS = (s == 0) ? Cfg::kColS0 : Cfg::kColS1;
+            const uint32_t colO = (s == 0) ? Cfg::kColO0 : Cfg::kColO1;
+            if (act_j) {  // O_s += P_s(j) V_j
+              const uint32_t it = it_base + 2u * (j - g.lo_all) + 1u;
+              const uint32_t slot = it % Cfg::kStages;
+              if (!mbar_wait(&p_full[s], n_p[s] & 1, abort_flag)) { ok = false; break; }
+              ++n_p[s];
+              if (!mbar_wait(&kv_full[slot], (it / Cfg::kStages) & 1, abort_flag)) { ok = false; break; }
+              tc_fence_after();
+              const uint32_t va = kv_addr + slot * Cfg::kTileBytes;
+#pragma unroll
+              for (int kk = 0; kk < kBlockN / 16; ++kk) {
+                umma_ts(tmem_base + colO, tmem_base + colS + kk * 8,
+                        umma_desc_sw128(va + kk * 2048, Cfg::kPanelBytes, 1024), idesc_pv,
+                        (j > g.lo[s] || kk > 0) ? 1u : 0u);
+              }
+              if (!other_j) umma_commit(&kv_empty[slot]);
+              if (j + 1 == g.hi[s]) umma_commit(&o_full[s]);
+            }
+            if (act_n) {  // S_s = Q_s K_{j+1}^T
+              const uint32_t it = it_base + 2u * (j + 1 - g.lo_all);
+              const uint32_t slot = it % Cfg::kStages;
+              if (j + 1 == g.lo[s]) {
+                if (!mbar_wait(&q_full[s], n_q[s] & 1, abort_flag)) { ok = false; break; }
+                ++n_q[s];
+              }
+              if (!mbar_wait(&kv_full[slot], (it / Cfg::kStages) & 1, abort_flag)) { ok = false; break; }
+              tc_fence_after();
+              const uint32_t qa = q_addr + s * Cfg::kTileBytes;
+              const uint32_t ka = kv_addr + slot * Cfg::kTileBytes;
+#pragma unroll
+              for (int k = 0; k < D / 16; ++k) {
+                const uint32_t off = (k / 4) * Cfg::kPanelBytes + (k % 4) * 32;
+                umma_ss(tmem_base + colS, umma_desc_sw128(qa + off, 16, 1024), umma_desc_sw128(ka + off, 16, 1024),
+                        idesc_qk, k > 0);
+              }
+              umma_commit(&s_full[s]);
+              if (!other_n) umma_commit(&kv_empty[slot]);
+              if (j + 2 == g.hi[s]) umma_commit(&q_empty[s]);
+            }
+          }
+        }
+        it_base += 2u * (g.hi_all - g.lo_all);
+      }
+    } else if (warp == 13 && lane == 0) {
+      // ===================================================================================
+      // TMA producer
+      // ===================================================================================
+      uint32_t it = 0;
+      uint32_t n_q[2] = {0, 0};
+      bool ok = true;
+      for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
+        const ItemGeom g = decode_item(item, p);
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          if (g.r1[s] < g.r0[s]) continue;
+          if (!mbar_wait(&q_empty[s], (n_q[s] & 1) ^ 1, abort_flag)) { ok = false; break; }
+          ++n_q[s];
+          mbar_arrive_expect_tx(&q_full[s], Cfg::kTileBytes);
+          tma_load_4d(sQ + s * Cfg::kTileBytes, &mapQ, &q_full[s], 0, g.r0[s], 0, g.bh);
+        }
+        for (int j = g.lo_all; j < g.hi_all && ok; ++j) {
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            const uint32_t slot = it % Cfg::kStages;
+            if (!mbar_wait(&kv_empty[slot], ((it / Cfg::kStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
+            mbar_arrive_expect_tx(&kv_full[slot], Cfg::kTileBytes);
+            tma_load_4d(sKV + slot * Cfg::kTileBytes, t == 0 ? &mapK : &mapV, &kv_full[slot], 0, j * kBlockN, 0, g.bh);
+            ++it;
+          }
+        }
+      }
+      if (!ok) {
+        // give-up path: let loads that are still in flight land before the CTA retires
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && *abort_flag != 0) atomicExch(p.status, 1);
+  if (warp == 12) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+}
+
+}  // namespace fa
