@@ -1,0 +1,380 @@
+"""Benchmark of the attention-forward hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload: the long-context causal configuration that is defined for 1/2/4/8 GPUs
+(fp16 Q/K/V of shape [B=8, H=64, N=32768, d=128], causal, scale 1/sqrt(128)), sharded over the
+independent (batch, head) axis: rank r of N owns a contiguous slab of 512/N heads, there is no
+collective on the data path (total work is fixed, so this is strong scaling). One "step" is one
+forward over the rank's slab. Inputs are synthetic: i.i.d. N(0,1), seeded, generated on the
+device; every slab (>= 2 GiB) is larger than L2, so no flush is needed between steps.
+
+Printed (rank 0, one JSON line): the whole-job TFLOP/s with inputs resident in HBM (`value`),
+the same through the host-buffer C-ABI call with uploads and download inside the timed region
+(`e2e`), the roofline of the kernel, the CPU baseline, SM clocks during the timed region, and
+the smaller single-GPU configurations for context (`per_config`, N=1 only).
+
+`--impl reference` times the reference's own CPU attention (compiled from its sources into
+oracle/_ref when they were available at build time, else the C restatement) on all host cores,
+on a bounded sample of the same workload.
+"""
+import argparse
+import ctypes
+import json
+import math
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+WORKLOAD = dict(name="C5 long-context causal", B=8, H=64, N=32768, d=128, causal=True, wl=-1, wr=-1)
+OTHER_CONFIGS = [
+    dict(name="C1", B=1, H=4, N=512, d=64, causal=False, wl=-1, wr=-1),
+    dict(name="C2", B=4, H=16, N=2048, d=64, causal=True, wl=-1, wr=-1),
+    dict(name="C3", B=2, H=32, N=8192, d=128, causal=True, wl=-1, wr=-1),
+    dict(name="C4", B=4, H=16, N=16384, d=128, causal=True, wl=1024, wr=-1),
+]
+METRIC = "fwd attention TFLOP/s (whole job; FLOPs = 4*B*H*N^2*d, halved for causal)"
+FALLBACK_TFLOPS = 1590.0  # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
+
+
+def env_int(name, default):
+    try:
+        return int(os.environ.get(name, default))
+    except ValueError:
+        return default
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            p = json.load(open(path))
+            return dict(burst=float(p["bf16_tflops"]), sustained=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                        source="measured")
+        except Exception:
+            pass
+    return dict(burst=FALLBACK_TFLOPS, sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.out,
+                                         stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        rows = []
+        for line in open(self.path):
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) >= 9:
+                try:
+                    rows.append((float(parts[1]), float(parts[2]), float(parts[3]), parts[5], parts[6], parts[7], parts[8]))
+                except ValueError:
+                    pass
+        os.unlink(self.path)
+        if not rows:
+            return None
+        pmax = max(r[2] for r in rows)
+        loaded = [r for r in rows if r[2] >= 0.5 * pmax] or rows
+        clocks = sorted(r[0] for r in loaded)
+        reasons = []
+        for name, idx in (("hw_slowdown", 3), ("hw_thermal_slowdown", 4), ("sw_thermal_slowdown", 5), ("sw_power_cap", 6)):
+            if any(r[idx].lower().startswith("active") for r in loaded):
+                reasons.append(name)
+        return dict(sm_mhz=clocks[len(clocks) // 2], sm_max_mhz=rows[0][1], power_w_max=pmax, samples=len(loaded),
+                    reasons=reasons)
+
+
+def shard(rank, world, total_heads):
+    """Contiguous slab of the flattened (batch, head) axis owned by `rank`: [begin, end)."""
+    base, rem = divmod(total_heads, world)
+    begin = rank * base + min(rank, rem)
+    return begin, begin + base + (1 if rank < rem else 0)
+
+
+def cpu_sample(ob, cfg, cores, seconds_hint=None):
+    """One bounded CPU sample of the workload: the causal prefix (first n rows and keys) of `cores`
+    heads, one head per host thread. For causal attention the first n rows of a head depend on
+    the first n keys only, so this is exactly the work of those rows. Returns (seconds, flops
+    by the metric's causal count, description, kind)."""
+    import numpy as np
+
+    n = 1024
+    d = cfg["d"]
+    rng = np.random.default_rng(26)
+    q, k, v = (rng.standard_normal((1, cores, n, d), dtype=np.float32).astype(np.float16) for _ in range(3))
+    if ob.ref_available():
+        kind = "reference"
+        t0 = time.perf_counter()
+        ob.reference_attention(q, k, v, causal=True, window_size=-1, nthreads=cores)
+        dt = time.perf_counter() - t0
+    else:
+        kind = "port"
+        t0 = time.perf_counter()
+        ob.attention(q, k, v, causal=True, nthreads=cores)
+        dt = time.perf_counter() - t0
+    flops = 2.0 * cores * n * n * d
+    desc = (f"first {n} query rows (causal prefix) of {cores} heads of the workload, d={d}, one head per thread, "
+            f"{'unmodified reference attention_forward_cpu' if kind == 'reference' else 'C restatement of it'}; "
+            f"dense-count rate {2 * flops / dt / 1e9:.3f} GFLOP/s")
+    return dt, flops, desc, kind
+
+
+def host_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def run_reference(args):
+    rank = env_int("RANK", 0)
+    if rank != 0:
+        return 0
+    ob = entry.load_oracle()
+    cores = host_cores()
+    for _ in range(args.warmup):
+        cpu_sample(ob, WORKLOAD, cores)
+    total_t, total_f, desc, kind = 0.0, 0.0, "", "port"
+    for _ in range(args.steps):
+        dt, fl, desc, kind = cpu_sample(ob, WORKLOAD, cores)
+        total_t += dt
+        total_f += fl
+    value = total_f / total_t / 1e12
+    line = dict(impl="reference", metric=METRIC, value=value, unit="TFLOP/s", n_gpus=args.gpus, steps=args.steps,
+                warmup=args.warmup, ms_per_step=1e3 * total_t / args.steps, higher_is_better=True, scaling="strong",
+                vs_baseline=None, dtype="f16", data="synthetic",
+                config=dict(workload="B8 H64 N32768 d128 causal fp16, sharded by (batch, head); CPU arm runs a bounded sample",
+                            timing="host wall clock around each sample"),
+                cpu_baseline=dict(value=value, unit="TFLOP/s", cores=cores, kind=kind, sample=desc),
+                e2e=dict(value=value, unit="TFLOP/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
+    print(json.dumps(line))
+    return 0
+
+
+def time_config(pkg, torch, cfg, heads, iters, warmup, stream):
+    """Device-resident timing of one configuration on the current GPU (heads = this rank's slab)."""
+    N, d = cfg["N"], cfg["d"]
+    g = torch.Generator(device="cuda")
+    g.manual_seed(26)
+    q, k, v = (torch.randn((1, heads, N, d), generator=g, device="cuda", dtype=torch.float16) for _ in range(3))
+    o = torch.empty_like(q)
+    args = (q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), 1, heads, N, d)
+    kw = dict(is_causal=cfg["causal"], window_left=cfg["wl"], window_right=cfg["wr"], stream=stream.cuda_stream)
+    for _ in range(warmup):
+        pkg.flash_forward(*args, **kw)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    stream.synchronize()
+    e0.record(stream)
+    for _ in range(iters):
+        pkg.flash_forward(*args, **kw)
+    e1.record(stream)
+    e1.synchronize()
+    pkg.check(stream.cuda_stream)
+    ms = e0.elapsed_time(e1) / iters
+    fl = pkg.flops(1, heads, N, d, cfg["causal"], cfg["wl"], cfg["wr"])
+    return ms, fl, (q, k, v, o)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--heads-per-gpu", type=int, default=0, help="override the slab size (debugging only)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    rank, world, local = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a GPU: the attention forward has no CPU path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    pkg = entry.load_package()
+    pkg.lib()  # fails loudly if the CUDA library is missing
+    stream = torch.cuda.Stream()
+
+    cfg = WORKLOAD
+    total_heads = cfg["B"] * cfg["H"]
+    h0, h1 = shard(rank, world, total_heads)
+    heads = args.heads_per_gpu or (h1 - h0)
+    N, d = cfg["N"], cfg["d"]
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident throughput -------------------------------------------------------
+    g = torch.Generator(device="cuda")
+    g.manual_seed(1000 + h0)
+    q, k, v = (torch.randn((1, heads, N, d), generator=g, device="cuda", dtype=torch.float16) for _ in range(3))
+    o = torch.empty_like(q)
+    ptrs = (q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), 1, heads, N, d)
+    kw = dict(is_causal=cfg["causal"], window_left=cfg["wl"], window_right=cfg["wr"], stream=stream.cuda_stream)
+    for _ in range(args.warmup):
+        pkg.flash_forward(*ptrs, **kw)
+    pkg.check(stream.cuda_stream)
+    sampler = ClockSampler(local) if rank == 0 else None
+    barrier()
+    if sampler:
+        sampler.start()
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    evs[0].record(stream)
+    for i in range(args.steps):
+        pkg.flash_forward(*ptrs, **kw)
+        evs[i + 1].record(stream)
+    evs[-1].synchronize()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    pkg.check(stream.cuda_stream)
+    total_ms = evs[0].elapsed_time(evs[-1])
+    kernel_ms = sum(evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps)) / args.steps
+    t = torch.tensor([total_ms], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    flops_rank = pkg.flops(1, heads, N, d, cfg["causal"], cfg["wl"], cfg["wr"])
+    fl = torch.tensor([flops_rank], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(fl, op=dist.ReduceOp.SUM)
+    flops_job = float(fl.item())
+    ms_per_step = total_ms / args.steps
+    value = flops_job / (ms_per_step * 1e-3) / 1e12
+
+    # ---- sanity: sampled rows of one head against the CPU oracle (outside every timed region) ----
+    parity = None
+    if rank == 0:
+        ob = entry.load_oracle()
+        rows = np.unique(np.concatenate([np.arange(0, 130), np.arange(N - 64, N),
+                                         np.random.default_rng(5).integers(0, N, 64)])).astype(np.int32)
+        hq, hk, hv, ho = (x[0, heads - 1].cpu().numpy() for x in (q, k, v, o))
+        want = ob.attention_rows(hq, hk, hv, rows, causal=cfg["causal"], window_left=cfg["wl"], window_right=cfg["wr"])
+        mx, mean, nans = ob.abs_error(ho[rows], want)
+        parity = dict(rows=int(rows.size), max_abs=mx, mean_abs=mean, nan=nans, ok=bool(nans == 0 and mx <= 2e-3 and mean <= 2e-4))
+
+    # ---- end to end: host buffers through the C ABI, copies inside the timed region ----------
+    chunk = min(32, heads)
+    ws_bytes = pkg.host_workspace_bytes(N, d, chunk)
+    hq, hk, hv = (torch.empty((1, heads, N, d), dtype=torch.float16, pin_memory=True) for _ in range(3))
+    ho = torch.empty((1, heads, N, d), dtype=torch.float16, pin_memory=True)
+    hq.copy_(q); hk.copy_(k); hv.copy_(v)
+    o_dev_copy = o[0, 0, :256].cpu()
+    del q, k, v, o
+    torch.cuda.empty_cache()
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+    e2e_steps = max(2, min(args.steps, 8))
+
+    def e2e_step():
+        pkg.flash_forward_host(hq.data_ptr(), hk.data_ptr(), hv.data_ptr(), ho.data_ptr(), 1, heads, N, d,
+                               ws.data_ptr(), ws_bytes, chunk, is_causal=cfg["causal"], window_left=cfg["wl"],
+                               window_right=cfg["wr"])
+
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    t = torch.tensor([dt], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_s = float(t.item()) / e2e_steps
+    e2e_ok = bool(torch.equal(ho[0, 0, :256], o_dev_copy))
+    bytes_in = 3 * heads * N * d * 2 * world
+    bytes_out = heads * N * d * 2 * world
+    e2e = dict(value=flops_job / e2e_s / 1e12, unit="TFLOP/s", h2d_bytes_per_step=bytes_in, d2h_bytes_per_step=bytes_out,
+               steps=e2e_steps, ms_per_step=1e3 * e2e_s, matches_device_path=e2e_ok,
+               api="flash_forward_host (pinned host buffers, chunked upload/kernel/download pipeline)")
+    del ws, hq, hk, hv, ho
+    torch.cuda.empty_cache()
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return 0
+
+    # ---- rank 0 only: roofline, other configurations, CPU baseline ---------------------------
+    pk = peaks()
+    achieved = flops_rank / (kernel_ms * 1e-3) / 1e12
+    # each timed step is one ~0.1 s launch inside a seconds-long loop under the power cap
+    roofline = dict(bound="tensor", achieved=achieved, peak=pk["sustained"], unit="TFLOP/s", frac=achieved / pk["sustained"],
+                    traffic=None, peak_source=f"{pk['source']} bf16 GEMM, sustained figure (kernel timed inside a long loop)",
+                    frac_of_burst_peak=achieved / pk["burst"], burst_peak=pk["burst"],
+                    kernel="fwd_persistent_kernel<128>", launch_ms=kernel_ms, flops_per_launch=flops_rank)
+    per_config = []
+    cpu_baseline = None
+    if world == 1:
+        for c in OTHER_CONFIGS:
+            bh = c["B"] * c["H"]
+            ms, fl_c, _ = time_config(pkg, torch, c, bh, 20, 5, stream)
+            tf = fl_c / (ms * 1e-3) / 1e12
+            per_config.append(dict(name=c["name"], shape=f"B{c['B']} H{c['H']} N{c['N']} d{c['d']}", causal=c["causal"],
+                                   window_left=c["wl"], ms=ms, tflops=tf, frac_of_burst_peak=tf / pk["burst"]))
+            torch.cuda.empty_cache()
+        ob = entry.load_oracle()
+        cores = host_cores()
+        dt_cpu, fl_cpu, desc, kind = cpu_sample(ob, cfg, cores)
+        cpu_baseline = dict(value=fl_cpu / dt_cpu / 1e12, unit="TFLOP/s", cores=cores, kind=kind, sample=desc,
+                            seconds=dt_cpu)
+    line = dict(metric=METRIC, value=value, unit="TFLOP/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
+                ms_per_step=ms_per_step, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="f16",
+                data="synthetic",
+                config=dict(workload="B8 H64 N32768 d128 causal fp16 (long-context config), sharded by (batch, head)",
+                            heads_per_gpu=heads, global_heads=total_heads if not args.heads_per_gpu else heads * world,
+                            seq_len=N, head_dim=d, parallelism=f"head-shard x{world}, no collective",
+                            l2="inputs larger than L2 (>= 2 GiB per tensor per GPU), no flush",
+                            timing="CUDA events on the launch stream, max over ranks"),
+                roofline=roofline, cpu_baseline=cpu_baseline, e2e=e2e, clocks=clocks, gpu_launches=args.steps * world,
+                parity=parity, per_config=per_config, tflops_per_gpu=value / world)
+    print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

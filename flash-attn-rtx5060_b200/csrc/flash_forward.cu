@@ -144,6 +144,38 @@ int launch_persistent(DeviceState* s, const CUtensorMap& mq, const CUtensorMap& 
   return FA_OK;
 }
 
+// ---- host-buffer entry point -----------------------------------------------------------
+// Per device: three streams (upload, compute, download) and the events that chain them.
+struct HostPipe {
+  bool ready = false;
+  cudaStream_t up = nullptr, run = nullptr, down = nullptr;
+  cudaEvent_t in_ready[2] = {}, done[2] = {}, out_done[2] = {};
+};
+HostPipe g_pipe[kMaxDevices];
+
+int host_pipe(HostPipe** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail_cuda("cudaGetDevice", e);
+  if (dev < 0 || dev >= kMaxDevices) return fail(FA_UNSUPPORTED, "device ordinal out of range");
+  HostPipe& hp = g_pipe[dev];
+  if (!hp.ready) {
+    if ((e = cudaStreamCreateWithFlags(&hp.up, cudaStreamNonBlocking)) != cudaSuccess ||
+        (e = cudaStreamCreateWithFlags(&hp.run, cudaStreamNonBlocking)) != cudaSuccess ||
+        (e = cudaStreamCreateWithFlags(&hp.down, cudaStreamNonBlocking)) != cudaSuccess)
+      return fail_cuda("cudaStreamCreate", e);
+    for (int i = 0; i < 2; ++i) {
+      if ((e = cudaEventCreateWithFlags(&hp.in_ready[i], cudaEventDisableTiming)) != cudaSuccess ||
+          (e = cudaEventCreateWithFlags(&hp.done[i], cudaEventDisableTiming)) != cudaSuccess ||
+          (e = cudaEventCreateWithFlags(&hp.out_done[i], cudaEventDisableTiming)) != cudaSuccess)
+        return fail_cuda("cudaEventCreate", e);
+    }
+    hp.ready = true;
+  }
+  *out = &hp;
+  return FA_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -164,6 +196,22 @@ double flash_forward_flops(int batch, int heads, int seqlen, int head_dim, int i
     if (hi >= lo) pairs += hi - lo + 1;
   }
   return 4.0 * bh * pairs * d;
+}
+
+int flash_forward_kv_range(int seqlen, int is_causal, int window_left, int window_right, int row_begin,
+                           int row_end, int* tile_begin, int* tile_end, int* masked_tiles) {
+  if (seqlen <= 0 || row_begin < 0 || row_end < row_begin || row_end >= seqlen || !tile_begin || !tile_end ||
+      !masked_tiles)
+    return fail(FA_INVALID_ARG, "bad row range");
+  const int wl = window_left < 0 ? -1 : window_left;
+  const int wr = fa::eff_window_right(is_causal, window_right < 0 ? -1 : window_right);
+  *tile_begin = fa::kv_tile_begin(row_begin, wl);
+  *tile_end = fa::kv_tile_end(row_end, wr, seqlen);
+  int masked = 0;
+  for (int j = *tile_begin; j < *tile_end; ++j)
+    masked += fa::kv_tile_needs_mask(j * fa::kBlockN, row_begin, row_end, wl, wr, seqlen) ? 1 : 0;
+  *masked_tiles = masked;
+  return FA_OK;
 }
 
 int flash_forward_ex(const void* q, const void* k, const void* v, void* o, int batch, int heads, int seqlen,
@@ -266,6 +314,64 @@ int run_flash_attention_c(int B, int N, int S, int d, void* Q, void* K, void* V,
   return rc;
 }
 
+size_t flash_forward_host_workspace_bytes(int seqlen, int head_dim, int chunk_heads) {
+  if (seqlen <= 0 || head_dim <= 0 || chunk_heads <= 0) return 0;
+  return (size_t)2 * 4 * (size_t)chunk_heads * seqlen * head_dim * 2;
+}
+
+int flash_forward_host(const void* q_host, const void* k_host, const void* v_host, void* o_host, int batch,
+                       int heads, int seqlen, int head_dim, float softmax_scale, int is_causal, int window_left,
+                       int window_right, void* workspace, size_t workspace_bytes, int chunk_heads) {
+  if (!q_host || !k_host || !v_host || !o_host) return fail(FA_INVALID_ARG, "null host pointer");
+  if (batch <= 0 || heads <= 0 || seqlen <= 0) return fail(FA_INVALID_ARG, "batch, heads and seqlen must be positive");
+  if (head_dim != 64 && head_dim != 128) return fail(FA_UNSUPPORTED, "head_dim must be 64 or 128");
+  if (chunk_heads <= 0) return fail(FA_INVALID_ARG, "chunk_heads must be positive");
+  if (!workspace || workspace_bytes < flash_forward_host_workspace_bytes(seqlen, head_dim, chunk_heads))
+    return fail(FA_INVALID_ARG, "device workspace is null or smaller than flash_forward_host_workspace_bytes()");
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(FA_INVALID_ARG, "workspace must be 256-byte aligned");
+  HostPipe* hp = nullptr;
+  int rc = host_pipe(&hp);
+  if (rc != FA_OK) return rc;
+
+  const long long bh = (long long)batch * heads;
+  const size_t head_bytes = (size_t)seqlen * head_dim * 2;
+  const size_t slot_bytes = (size_t)chunk_heads * head_bytes;
+  char* ws = static_cast<char*>(workspace);
+  auto dev_ptr = [&](int slot, int tensor) { return ws + ((size_t)slot * 4 + tensor) * slot_bytes; };
+  const char* src[3] = {static_cast<const char*>(q_host), static_cast<const char*>(k_host),
+                        static_cast<const char*>(v_host)};
+  cudaError_t e;
+  int n = 0;
+  for (long long h0 = 0; h0 < bh; h0 += chunk_heads, ++n) {
+    const int slot = n & 1;
+    const int nh = (int)((bh - h0 < chunk_heads) ? (bh - h0) : chunk_heads);
+    const size_t bytes = (size_t)nh * head_bytes;
+    // the slot is free once the download that used it two chunks ago has finished
+    if (n >= 2 && (e = cudaStreamWaitEvent(hp->up, hp->out_done[slot], 0)) != cudaSuccess)
+      return fail_cuda("cudaStreamWaitEvent", e);
+    for (int t = 0; t < 3; ++t)
+      if ((e = cudaMemcpyAsync(dev_ptr(slot, t), src[t] + (size_t)h0 * head_bytes, bytes, cudaMemcpyHostToDevice,
+                               hp->up)) != cudaSuccess)
+        return fail_cuda("cudaMemcpyAsync(H2D)", e);
+    cudaEventRecord(hp->in_ready[slot], hp->up);
+    cudaStreamWaitEvent(hp->run, hp->in_ready[slot], 0);
+    if (n >= 2) cudaStreamWaitEvent(hp->run, hp->out_done[slot], 0);
+    rc = flash_forward(dev_ptr(slot, 0), dev_ptr(slot, 1), dev_ptr(slot, 2), dev_ptr(slot, 3), 1, nh, seqlen, head_dim,
+                       softmax_scale, is_causal, window_left, window_right, hp->run);
+    if (rc != FA_OK) break;
+    cudaEventRecord(hp->done[slot], hp->run);
+    cudaStreamWaitEvent(hp->down, hp->done[slot], 0);
+    if ((e = cudaMemcpyAsync(static_cast<char*>(o_host) + (size_t)h0 * head_bytes, dev_ptr(slot, 3), bytes,
+                             cudaMemcpyDeviceToHost, hp->down)) != cudaSuccess)
+      return fail_cuda("cudaMemcpyAsync(D2H)", e);
+    cudaEventRecord(hp->out_done[slot], hp->down);
+  }
+  cudaStreamSynchronize(hp->up);
+  int rc_run = flash_forward_check(hp->run);
+  if ((e = cudaStreamSynchronize(hp->down)) != cudaSuccess && rc == FA_OK) rc = fail_cuda("cudaStreamSynchronize", e);
+  return rc != FA_OK ? rc : rc_run;
+}
+
 int flash_forward_shutdown(void) {
   int prev = 0;
   if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
@@ -279,6 +385,19 @@ int flash_forward_shutdown(void) {
     }
     s.probed = false;
     for (bool& b : s.attr_set) b = false;
+    HostPipe& hp = g_pipe[d];
+    if (hp.ready) {
+      cudaSetDevice(d);
+      cudaStreamDestroy(hp.up);
+      cudaStreamDestroy(hp.run);
+      cudaStreamDestroy(hp.down);
+      for (int i = 0; i < 2; ++i) {
+        cudaEventDestroy(hp.in_ready[i]);
+        cudaEventDestroy(hp.done[i]);
+        cudaEventDestroy(hp.out_done[i]);
+      }
+      hp = HostPipe();
+    }
   }
   if (prev >= 0) cudaSetDevice(prev);
   return FA_OK;

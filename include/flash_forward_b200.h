@@ -58,6 +58,18 @@ int flash_forward_ex(const void* q, const void* k, const void* v, void* o, int b
                      int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,
                      void* stream, int kernel, int variant, float* dbg);
 
+/* The same forward for callers that hold Q, K, V and want O in HOST memory: the flow of the
+ * reference's driver (src/main.cu:83-85 upload, :99 run, :101 download) as one blocking call.
+ * The (batch, head) axis is cut into chunks of `chunk_heads` heads; upload, kernel and download
+ * of successive chunks overlap on three internal streams through a two-slot device workspace
+ * of flash_forward_host_workspace_bytes() bytes that the caller provides (256-byte aligned).
+ * Pinned host buffers give full overlap; pageable ones work but serialise. Returns after O is
+ * complete in o_host, with FA_DEVICE_TIMEOUT if a device-side wait gave up. */
+int flash_forward_host(const void* q_host, const void* k_host, const void* v_host, void* o_host, int batch,
+                       int heads, int seqlen, int head_dim, float softmax_scale, int is_causal, int window_left,
+                       int window_right, void* workspace, size_t workspace_bytes, int chunk_heads);
+size_t flash_forward_host_workspace_bytes(int seqlen, int head_dim, int chunk_heads);
+
 /* Waits for `stream`, then reads and clears the current device's status word. Returns FA_OK,
  * FA_DEVICE_TIMEOUT, or FA_CUDA_ERROR. Replaces the reference's CUDA_CHECK(cudaDeviceSynchronize())
  * + exit (src/flash_forward.h:654-655). */
@@ -78,10 +90,19 @@ int run_flash_attention_c(int B, int N, int S, int d, void* Q, void* K, void* V,
 /* Message for the last non-OK status returned on the calling thread ("" if none). */
 const char* flash_forward_last_error(void);
 
-/* Algorithmic work of one call: FLOPs = 4 * (visible query-key pairs) * head_dim summed over
- * batch*heads, the count the throughput figures use (4*B*H*N^2*d dense, halved for causal). */
+/* Algorithmic work of one call, the count the throughput figures use: 4*B*H*N^2*d without a
+ * window, exactly half of that when causal; with a window, 4 * head_dim * (visible query-key
+ * pairs) summed over batch*heads. Needs no GPU. */
 double flash_forward_flops(int batch, int heads, int seqlen, int head_dim, int is_causal, int window_left,
                            int window_right);
+
+/* Host-side view of the kernel's tile plan: the kv tiles (128 keys each) that query rows
+ * [row_begin, row_end] read are [*tile_begin, *tile_end), of which *masked_tiles are cut by a
+ * mask boundary or by the end of the sequence and take the per-element predicate; all others
+ * run unmasked. Same bounds as the reference's Schedule::next (src/flash_forward.h:52-61),
+ * extended to a two-sided window. Needs no GPU. */
+int flash_forward_kv_range(int seqlen, int is_causal, int window_left, int window_right, int row_begin,
+                           int row_end, int* tile_begin, int* tile_end, int* masked_tiles);
 
 /* Frees the per-device status words this library allocated. Optional. */
 int flash_forward_shutdown(void);

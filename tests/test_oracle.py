@@ -1,0 +1,83 @@
+"""CPU tests of the oracle: the C restatement against the golden vectors made by the reference's
+own attention_forward_cpu (src/main.cu:159-268), against that function itself where it was
+compiled, and the internal consistency of the restatement (row API, threads, fp16 conversion)."""
+import os
+
+import numpy as np
+import pytest
+
+from conftest import GOLDEN_DIR, golden_cases, make_inputs
+
+
+@pytest.mark.parametrize("fname", golden_cases())
+def test_port_matches_golden_bit_for_bit(ob, fname):
+    z = np.load(os.path.join(GOLDEN_DIR, fname))
+    q, k, v = (z[n].view(np.float16) for n in ("q", "k", "v"))
+    w = int(z["window"])
+    slopes = z["slopes"] if int(z["alibi"]) else None
+    got = ob.attention(q, k, v, causal=bool(int(z["causal"])), window_left=w, window_right=w, alibi_slopes=slopes)
+    want = z["out"]
+    assert np.array_equal(got.view(np.uint16), want), f"{(got.view(np.uint16) != want).sum()} elements differ"
+
+
+@pytest.mark.parametrize("case", [
+    (1, 2, 192, 64, False, -1, False, "normal"),
+    (1, 1, 320, 128, True, -1, False, "normal"),
+    (2, 1, 256, 64, True, 64, False, "normal"),
+    (1, 1, 200, 64, False, 33, True, "normal"),
+    (1, 1, 128, 128, False, -1, False, "uniform"),
+])
+def test_port_matches_compiled_reference(ob, case):
+    if not ob.ref_available():
+        pytest.skip("oracle/_ref was not built (reference sources absent)")
+    B, H, N, d, causal, w, alibi, dist = case
+    q, k, v = make_inputs(101, B, H, N, d, dist)
+    slopes = np.array([-(2.0 ** (-8.0 / H * (i + 1))) for i in range(H)], dtype=np.float32) if alibi else None
+    want = ob.reference_attention(q, k, v, causal, w, alibi_slopes=slopes)
+    got = ob.attention(q, k, v, causal=causal, window_left=w, window_right=w, alibi_slopes=slopes)
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+
+
+def test_rows_api_equals_full(ob):
+    q, k, v = make_inputs(7, 1, 1, 300, 64)
+    full = ob.attention(q, k, v, causal=True, window_left=100, window_right=-1, nthreads=1)
+    rows = np.array([0, 1, 99, 100, 101, 127, 128, 129, 299], dtype=np.int32)
+    part = ob.attention_rows(q[0, 0], k[0, 0], v[0, 0], rows, causal=True, window_left=100, window_right=-1)
+    assert np.array_equal(part.view(np.uint16), full[0, 0][rows].view(np.uint16))
+
+
+def test_threads_do_not_change_bits(ob):
+    q, k, v = make_inputs(8, 2, 3, 160, 64)
+    a = ob.attention(q, k, v, causal=True, nthreads=1)
+    b = ob.attention(q, k, v, causal=True, nthreads=4)
+    assert np.array_equal(a.view(np.uint16), b.view(np.uint16))
+
+
+def test_one_sided_window_is_causal_plus_symmetric(ob):
+    # the reference expresses "left w, right 0" as causal AND symmetric window w (mask.h:15,:43)
+    q, k, v = make_inputs(9, 1, 1, 256, 64)
+    a = ob.attention(q, k, v, causal=True, window_left=50, window_right=50)
+    b = ob.attention(q, k, v, causal=False, window_left=50, window_right=0)
+    assert np.array_equal(a.view(np.uint16), b.view(np.uint16))
+
+
+def test_fp16_conversion_is_ieee_round_to_nearest_even(ob):
+    # abs_error converts with the oracle's own h2f; feeding every fp16 bit pattern against itself
+    # and against numpy's conversion pins h2f. f2h is pinned through attention of a one-key
+    # problem: softmax over a single key is exactly 1, so out = half(float(half(1) * v)) = v.
+    allh = np.arange(65536, dtype=np.uint16)
+    finite = allh[np.isfinite(allh.view(np.float16))]
+    mx, mean, nans = ob.abs_error(finite, finite)
+    assert mx == 0 and nans == 0
+    vals = finite[: (finite.size // 64) * 64].reshape(1, 1, -1, 64)
+    N = vals.shape[2]
+    q = np.zeros((1, 1, N, 64), np.float16)
+    out = ob.attention(q, q, vals.view(np.float16), causal=False, window_left=0, window_right=0)
+    assert np.array_equal(out.view(np.uint16) & 0x7FFF, vals & 0x7FFF)  # -0 may come back as +0
+
+
+def test_abs_error_metric(ob):
+    a = np.array([1.0, 2.0, 3.0, np.nan], dtype=np.float16)
+    b = np.array([1.5, 2.0, 2.0, 0.0], dtype=np.float16)
+    mx, mean, nans = ob.abs_error(a, b)
+    assert mx == 1.0 and nans == 1 and abs(mean - 1.5 / 4) < 1e-12
