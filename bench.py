@@ -213,6 +213,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--heads-per-gpu", type=int, default=0, help="override the slab size (debugging only)")
+    ap.add_argument("--case", default="", help="profiling aid: time only this smaller configuration (C1..C4) on one "
+                    "GPU, device-resident, and print a short JSON line that is not a benchmark line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
@@ -232,6 +234,13 @@ def main():
     pkg = entry.load_package()
     pkg.lib()  # fails loudly if the CUDA library is missing
     stream = torch.cuda.Stream()
+
+    if args.case:
+        c = next(x for x in OTHER_CONFIGS if x["name"] == args.case)
+        ms, fl_c, _ = time_config(pkg, torch, c, c["B"] * c["H"], args.steps, args.warmup, stream)
+        print(json.dumps(dict(case=c["name"], ms=ms, tflops=fl_c / (ms * 1e-3) / 1e12, steps=args.steps,
+                              note="profiling aid, not a benchmark line")))
+        return 0
 
     cfg = WORKLOAD
     total_heads = cfg["B"] * cfg["H"]

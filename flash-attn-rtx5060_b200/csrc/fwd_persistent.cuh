@@ -6,11 +6,12 @@
 //   warps 4-7   softmax of q tile 1
 //   warps 8-11  correction: rescales the running output in TMEM when a row max moved, and the
 //               epilogue (O / l -> fp16 -> global)
-//   warp 12     tensor-core issuer: one thread issues every tcgen05.mma
+//   warp 12     tensor-core issuer: the warp walks the schedule, one elected lane issues tcgen05.mma
 //   warp 13     TMA producer: Q tiles and the K/V tile ring
 //   warps 14-15 idle (they only donate registers)
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D); the fp16 P tile of a
-// stage overwrites the first 64 columns of its own S.
+// stage overwrites the first 64 columns of its own S and is handed to the tensor pipe in two
+// halves of 64 keys, so that P.V starts while the second half is still being exponentiated.
 //
 // Replaces the reference's forward_kernel, Schedule and SMem (src/flash_forward.h:22-366),
 // apply_mask (src/mask.h:10-84) and apply_softmax (src/softmax.h:9-86): same function, but
@@ -23,9 +24,29 @@
 #include "ptx.cuh"
 
 #ifndef FA_REG_SOFTMAX
-#define FA_REG_SOFTMAX 176
+#define FA_REG_SOFTMAX 168
 #define FA_REG_CORR 96
-#define FA_REG_MISC 64
+#define FA_REG_MISC 80
+#endif
+
+// Of every 8 pairs of scores, this many pairs take their 2^x from a polynomial on the FMA pipe
+// instead of the MUFU unit, whose 16 results per clock per SM would otherwise bound the kernel.
+#ifndef FA_EMU_PAIRS
+#define FA_EMU_PAIRS 0
+#endif
+
+// Optional timeline capture for kernel bring-up (compile with -DFA_TRACE and pass a dbg buffer):
+// CTA 0 records clock64() stamps of its first work item, 8 stamps per (role, iteration).
+#ifdef FA_TRACE
+#define FA_TR(cond, role, iter, slot)                                                             \
+  do {                                                                                            \
+    if (blockIdx.x == 0 && item == 0 && p.dbg != nullptr && (cond) && (iter) >= 0 && (iter) < 64) \
+      reinterpret_cast<long long*>(p.dbg)[((role) * 64 + (iter)) * 8 + (slot)] = clock64();      \
+  } while (0)
+#else
+#define FA_TR(cond, role, iter, slot) \
+  do {                                \
+  } while (0)
 #endif
 
 namespace fa {
@@ -41,7 +62,7 @@ struct PersistentCfg {
   static constexpr int kOffAlpha = kOffKV + kStages * kTileBytes;  // float[2][128]
   static constexpr int kOffRowSum = kOffAlpha + 2 * kBlockM * 4;   // float[2][128]
   static constexpr int kOffBars = kOffRowSum + 2 * kBlockM * 4;
-  static constexpr int kNumBars = 14 + 2 * kStages;
+  static constexpr int kNumBars = 16 + 2 * kStages;
   static constexpr int kOffMisc = kOffBars + kNumBars * 8;
   static constexpr int kSmemBytes = kOffMisc + 16;
   static constexpr uint32_t kTmemCols = 512;
@@ -84,6 +105,49 @@ __device__ __forceinline__ ItemGeom decode_item(int item, const FwdParams& p) {
   return g;
 }
 
+// 2^x for a pair of scores on the FMA pipe: round-to-nearest split x = n + f with f in [-0.5, 0.5],
+// degree-3 minimax polynomial for 2^f (relative error 7.5e-5, below half an fp16 ulp of P), and n
+// added into the exponent field. x is clamped at -120 so the exponent cannot wrap.
+__device__ __forceinline__ void exp2_poly_pair(float x0, float x1, float& e0, float& e1) {
+  const float kMagic = 12582912.f;  // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
+  x0 = fmaxf(x0, -120.f);
+  x1 = fmaxf(x1, -120.f);
+  const uint64_t x2 = f2_pack(x0, x1);
+  const uint64_t t2 = f2_add(x2, f2_pack(kMagic, kMagic));
+  const uint64_t n2 = f2_add(t2, f2_pack(-kMagic, -kMagic));
+  const uint64_t f2 = f2_fma(n2, f2_pack(-1.f, -1.f), x2);
+  uint64_t r2 = f2_fma(f2, f2_pack(0.05517147481441498f, 0.05517147481441498f),
+                       f2_pack(0.2426111102104187f, 0.2426111102104187f));
+  r2 = f2_fma(r2, f2, f2_pack(0.6932610273361206f, 0.6932610273361206f));
+  r2 = f2_fma(r2, f2, f2_pack(0.9999280571937561f, 0.9999280571937561f));
+  float t0, t1, r0, r1;
+  f2_unpack(t2, t0, t1);
+  f2_unpack(r2, r0, r1);
+  e0 = __uint_as_float(__float_as_uint(r0) + (__float_as_uint(t0) << 23));
+  e1 = __uint_as_float(__float_as_uint(r1) + (__float_as_uint(t1) << 23));
+}
+
+// exp2 of 64 scores (32 pairs) -> 32 packed fp16x2 words; adds the exponentials into two
+// (even, odd) pairs of partial row sums.
+template <bool kAllowPoly>
+__device__ __forceinline__ void exp_half_tile(const float* sc, uint64_t scale2, uint64_t negms2, uint32_t (&pk)[32],
+                                              uint64_t& lsum_a, uint64_t& lsum_b) {
+#pragma unroll
+  for (int c = 0; c < 32; ++c) {
+    float x0, x1, e0, e1;
+    f2_unpack(f2_fma(f2_pack(sc[2 * c], sc[2 * c + 1]), scale2, negms2), x0, x1);
+    if (kAllowPoly && (c % 8) < FA_EMU_PAIRS) {
+      exp2_poly_pair(x0, x1, e0, e1);
+    } else {
+      e0 = ex2_approx(x0);
+      e1 = ex2_approx(x1);
+    }
+    if (c & 1) lsum_b = f2_add(lsum_b, f2_pack(e0, e1));
+    else lsum_a = f2_add(lsum_a, f2_pack(e0, e1));
+    pk[c] = pack_f16x2(e0, e1);
+  }
+}
+
 template <int D>
 __global__ void __launch_bounds__(512, 1)
 fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
@@ -108,12 +172,13 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   uint64_t* q_full = bars;            // [2] TMA -> MMA
   uint64_t* q_empty = bars + 2;       // [2] MMA -> TMA
   uint64_t* s_full = bars + 4;        // [2] MMA -> softmax: S tile in TMEM
-  uint64_t* p_full = bars + 6;        // [2] softmax (P written) + correction (O rescaled) -> MMA
+  uint64_t* p_full = bars + 6;        // [2] softmax (first half of P) + correction (O rescaled) -> MMA
   uint64_t* alpha_ready = bars + 8;   // [2] softmax -> correction: rescale factors in smem
   uint64_t* l_ready = bars + 10;      // [2] softmax -> correction: final row sums in smem
   uint64_t* o_full = bars + 12;       // [2] MMA -> correction: last P.V of the item landed
-  uint64_t* kv_full = bars + 14;      // [kStages] TMA -> MMA
-  uint64_t* kv_empty = bars + 14 + Cfg::kStages;  // [kStages] MMA -> TMA
+  uint64_t* p_full2 = bars + 14;      // [2] softmax -> MMA: second half of P written
+  uint64_t* kv_full = bars + 16;      // [kStages] TMA -> MMA
+  uint64_t* kv_empty = bars + 16 + Cfg::kStages;  // [kStages] MMA -> TMA
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -128,6 +193,7 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       mbar_init(&q_empty[s], 1);
       mbar_init(&s_full[s], 1);
       mbar_init(&p_full[s], 8);  // one arrival per softmax warp and per correction warp
+      mbar_init(&p_full2[s], 4);
       mbar_init(&alpha_ready[s], 4);
       mbar_init(&l_ready[s], 4);
       mbar_init(&o_full[s], 1);
@@ -162,6 +228,7 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     const int row_l = tid & 127;
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32u;
     const uint32_t tS = tmem_addr(tmem_base, lane_base, s == 0 ? Cfg::kColS0 : Cfg::kColS1);
+    const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2);
     uint32_t n_s = 0;  // completed s_full phases
     bool ok = true;
     for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
@@ -179,6 +246,7 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         if (!mbar_wait_warp(&s_full[s], n_s & 1, abort_flag)) { ok = false; break; }
         ++n_s;
         tc_fence_after();
+        FA_TR(row_l == 0, s, j - j_lo, 0);
         uint32_t r0[32], r1[32], r2[32], r3[32];
         tmem_ld32(tS + 0, r0);
         tmem_ld32(tS + 32, r1);
@@ -189,6 +257,7 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         tmem_ld_fence(r1);
         tmem_ld_fence(r2);
         tmem_ld_fence(r3);
+        FA_TR(row_l == 0, s, j - j_lo, 1);
         float sc[kBlockN];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -198,7 +267,8 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           sc[96 + i] = __uint_as_float(r3[i]);
         }
         const int kv0 = j * kBlockN;
-        if (kv_tile_needs_mask(kv0, q_r0, q_r1, wl, wr, N)) {
+        const bool masked = kv_tile_needs_mask(kv0, q_r0, q_r1, wl, wr, N);
+        if (masked) {
           const int c_lo = (wl >= 0) ? row - wl - kv0 : -1;
           int c_hi = N - 1 - kv0;
           if (wr >= 0) c_hi = min(c_hi, row + wr - kv0);
@@ -206,15 +276,15 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           for (int c = 0; c < kBlockN; ++c)
             if (c < c_lo || c > c_hi) sc[c] = -INFINITY;
         }
-        float mx0 = sc[0], mx1 = sc[1], mx2 = sc[2], mx3 = sc[3];
+        float mx0 = m_run, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-        for (int c = 4; c < kBlockN; c += 4) {
-          mx0 = fmaxf(mx0, sc[c]);
-          mx1 = fmaxf(mx1, sc[c + 1]);
-          mx2 = fmaxf(mx2, sc[c + 2]);
-          mx3 = fmaxf(mx3, sc[c + 3]);
+        for (int c = 0; c < kBlockN; c += 8) {
+          mx0 = max3(mx0, sc[c], sc[c + 1]);
+          mx1 = max3(mx1, sc[c + 2], sc[c + 3]);
+          mx2 = max3(mx2, sc[c + 4], sc[c + 5]);
+          mx3 = max3(mx3, sc[c + 6], sc[c + 7]);
         }
-        const float m_new = fmaxf(fmaxf(m_run, fmaxf(mx0, mx1)), fmaxf(mx2, mx3));
+        const float m_new = max3(mx0, mx1, fmaxf(mx2, mx3));
         // Lazy rescale: keep the old reference max unless the true max moved by more than
         // kLazyLog2 (P then stays below 2^8, well inside fp16), or no finite score was seen yet.
         float alpha = 1.f;
@@ -228,33 +298,32 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         sAlpha[s * kBlockM + row_l] = alpha;
         __syncwarp();
         if (lane == 0) mbar_arrive(&alpha_ready[s]);
+        FA_TR(row_l == 0, s, j - j_lo, 2);
 
         const float neg_ms = -m_used * p.scale_log2;
-        float l0 = 0.f, l1 = 0.f;
+        const uint64_t negms2 = f2_pack(neg_ms, neg_ms);
+        uint64_t lsum_a = 0ull, lsum_b = 0ull;
         uint32_t pk0[32], pk1[32];
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const float e0 = ex2_approx(fmaf(sc[2 * c], p.scale_log2, neg_ms));
-          const float e1 = ex2_approx(fmaf(sc[2 * c + 1], p.scale_log2, neg_ms));
-          l0 += e0;
-          l1 += e1;
-          pk0[c] = pack_f16x2(e0, e1);
-        }
+        // masked tiles hold -inf scores, which only the MUFU path maps to 0
+        if (masked) exp_half_tile<false>(sc, scale2, negms2, pk0, lsum_a, lsum_b);
+        else exp_half_tile<true>(sc, scale2, negms2, pk0, lsum_a, lsum_b);
         tmem_st32(tS + 0, pk0);
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const float e0 = ex2_approx(fmaf(sc[64 + 2 * c], p.scale_log2, neg_ms));
-          const float e1 = ex2_approx(fmaf(sc[64 + 2 * c + 1], p.scale_log2, neg_ms));
-          l0 += e0;
-          l1 += e1;
-          pk1[c] = pack_f16x2(e0, e1);
-        }
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[s]);  // P of keys 0..63 is in TMEM
+        FA_TR(row_l == 0, s, j - j_lo, 3);
+        if (masked) exp_half_tile<false>(sc + 64, scale2, negms2, pk1, lsum_a, lsum_b);
+        else exp_half_tile<true>(sc + 64, scale2, negms2, pk1, lsum_a, lsum_b);
         tmem_st32(tS + 32, pk1);
+        float l0, l1;
+        f2_unpack(f2_add(lsum_a, lsum_b), l0, l1);
         l_run = l_run * alpha + (l0 + l1);
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&p_full[s]);
+        if (lane == 0) mbar_arrive(&p_full2[s]);  // P of keys 64..127
+        FA_TR(row_l == 0, s, j - j_lo, 4);
       }
       if (!ok) break;
       sRowSum[s * kBlockM + row_l] = l_run;
@@ -278,6 +347,7 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           if (j < g.lo[s] || j >= g.hi[s]) continue;
           if (!mbar_wait_warp(&alpha_ready[s], n_alpha[s] & 1, abort_flag)) { ok = false; break; }
           ++n_alpha[s];
+          FA_TR(row_l == 0, 2, j - g.lo_all, s * 4 + 0);
           const float alpha = sAlpha[s * kBlockM + row_l];
           if (j > g.lo[s] && __any_sync(0xffffffffu, alpha != 1.f)) {
             tc_fence_after();
@@ -297,6 +367,7 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&p_full[s]);
+          FA_TR(row_l == 0, 2, j - g.lo_all, s * 4 + 1);
         }
       }
       if (!ok) break;
@@ -335,14 +406,19 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     }
   } else {
     reg_dec<FA_REG_MISC>();
-    if (warp == 12 && lane == 0) {
+    if (warp == 12) {
       // ===================================================================================
-      // tensor-core issuer
+      // tensor-core issuer. The whole warp walks the schedule and waits, so that addresses and
+      // descriptors are warp-uniform values; one elected lane issues the tcgen05 instructions.
       // ===================================================================================
       constexpr uint32_t idesc_qk = umma_idesc_f16(kBlockM, kBlockN, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_f16(kBlockM, D, 0, 1);
+      // Descriptors are built once; per instruction only the 16-byte-unit start address moves.
+      const uint64_t kdesc0 = umma_desc_sw128(0, 16, 1024);               // K-major tiles (Q, K)
+      const uint64_t vdesc0 = umma_desc_sw128(0, Cfg::kPanelBytes, 1024);  // MN-major tile (V)
       const uint32_t q_addr = smem_u32(sQ);
       const uint32_t kv_addr = smem_u32(sKV);
+      const uint64_t qdesc[2] = {kdesc0 + (q_addr >> 4), kdesc0 + ((q_addr + Cfg::kTileBytes) >> 4)};
       uint32_t it_base = 0;  // ring position of K tile lo_all of the current item
       uint32_t n_p[2] = {0, 0}, n_q[2] = {0, 0};
       bool ok = true;
@@ -355,45 +431,65 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             const bool act_n = (j + 1 >= g.lo[s] && j + 1 < g.hi[s]);
             const bool other_j = (s == 0) && (j >= g.lo[1] && j < g.hi[1]);          // stage 1 still needs V_j
             const bool other_n = (s == 0) && (j + 1 >= g.lo[1] && j + 1 < g.hi[1]);  // stage 1 still needs K_j+1
+            // stage 0 already waited for this tile in the same round
+            const bool v_seen = (s == 1) && (j >= g.lo[0] && j < g.hi[0]);
+            const bool k_seen = (s == 1) && (j + 1 >= g.lo[0] && j + 1 < g.hi[0]);
             const uint32_t colS = (s == 0) ? Cfg::kColS0 : Cfg::kColS1;
             const uint32_t colO = (s == 0) ? Cfg::kColO0 : Cfg::kColO1;
-            if (act_j) {  // O_s += P_s(j) V_j
+            if (act_j) {  // O_s += P_s(j) V_j, in two halves of 64 keys as P arrives
               const uint32_t it = it_base + 2u * (j - g.lo_all) + 1u;
               const uint32_t slot = it % Cfg::kStages;
-              if (!mbar_wait(&p_full[s], n_p[s] & 1, abort_flag)) { ok = false; break; }
-              ++n_p[s];
-              if (!mbar_wait(&kv_full[slot], (it / Cfg::kStages) & 1, abort_flag)) { ok = false; break; }
+              const uint64_t vdesc = vdesc0 + ((kv_addr + slot * Cfg::kTileBytes) >> 4);
+              FA_TR(lane == 0, 3, j - g.lo_all + 1, s * 4 + 0);
+              if (!v_seen && !mbar_wait_warp(&kv_full[slot], (it / Cfg::kStages) & 1, abort_flag)) { ok = false; break; }
+              if (!mbar_wait_warp(&p_full[s], n_p[s] & 1, abort_flag)) { ok = false; break; }
               tc_fence_after();
-              const uint32_t va = kv_addr + slot * Cfg::kTileBytes;
+              FA_TR(lane == 0, 3, j - g.lo_all + 1, s * 4 + 1);
+              if (elect_one()) {
+                umma_ts(tmem_base + colO, tmem_base + colS, vdesc, idesc_pv, (j > g.lo[s]) ? 1u : 0u);
 #pragma unroll
-              for (int kk = 0; kk < kBlockN / 16; ++kk) {
-                umma_ts(tmem_base + colO, tmem_base + colS + kk * 8,
-                        umma_desc_sw128(va + kk * 2048, Cfg::kPanelBytes, 1024), idesc_pv,
-                        (j > g.lo[s] || kk > 0) ? 1u : 0u);
+                for (int kk = 1; kk < 4; ++kk)
+                  umma_ts(tmem_base + colO, tmem_base + colS + kk * 8, vdesc + kk * (2048 >> 4), idesc_pv, 1u);
               }
-              if (!other_j) umma_commit(&kv_empty[slot]);
-              if (j + 1 == g.hi[s]) umma_commit(&o_full[s]);
+              __syncwarp();
+              FA_TR(lane == 0, 3, j - g.lo_all + 1, s * 4 + 2);
+              if (!mbar_wait_warp(&p_full2[s], n_p[s] & 1, abort_flag)) { ok = false; break; }
+              ++n_p[s];
+              tc_fence_after();
+              FA_TR(lane == 0, 3, j - g.lo_all + 1, s * 4 + 3);
+              if (elect_one()) {
+#pragma unroll
+                for (int kk = 4; kk < 8; ++kk)
+                  umma_ts(tmem_base + colO, tmem_base + colS + kk * 8, vdesc + kk * (2048 >> 4), idesc_pv, 1u);
+                if (!other_j) umma_commit(&kv_empty[slot]);
+                if (j + 1 == g.hi[s]) umma_commit(&o_full[s]);
+              }
+              __syncwarp();
+              FA_TR(lane == 0, 5, j - g.lo_all + 1, s * 4 + 0);
             }
             if (act_n) {  // S_s = Q_s K_{j+1}^T
               const uint32_t it = it_base + 2u * (j + 1 - g.lo_all);
               const uint32_t slot = it % Cfg::kStages;
               if (j + 1 == g.lo[s]) {
-                if (!mbar_wait(&q_full[s], n_q[s] & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait_warp(&q_full[s], n_q[s] & 1, abort_flag)) { ok = false; break; }
                 ++n_q[s];
               }
-              if (!mbar_wait(&kv_full[slot], (it / Cfg::kStages) & 1, abort_flag)) { ok = false; break; }
+              if (!k_seen && !mbar_wait_warp(&kv_full[slot], (it / Cfg::kStages) & 1, abort_flag)) { ok = false; break; }
               tc_fence_after();
-              const uint32_t qa = q_addr + s * Cfg::kTileBytes;
-              const uint32_t ka = kv_addr + slot * Cfg::kTileBytes;
+              FA_TR(lane == 0, 5, j - g.lo_all + 1, s * 4 + 1);
+              const uint64_t kdesc = kdesc0 + ((kv_addr + slot * Cfg::kTileBytes) >> 4);
+              if (elect_one()) {
 #pragma unroll
-              for (int k = 0; k < D / 16; ++k) {
-                const uint32_t off = (k / 4) * Cfg::kPanelBytes + (k % 4) * 32;
-                umma_ss(tmem_base + colS, umma_desc_sw128(qa + off, 16, 1024), umma_desc_sw128(ka + off, 16, 1024),
-                        idesc_qk, k > 0);
+                for (int k = 0; k < D / 16; ++k) {
+                  const uint32_t off = ((k / 4) * Cfg::kPanelBytes + (k % 4) * 32) >> 4;
+                  umma_ss(tmem_base + colS, qdesc[s] + off, kdesc + off, idesc_qk, k > 0 ? 1u : 0u);
+                }
+                umma_commit(&s_full[s]);
+                if (!other_n) umma_commit(&kv_empty[slot]);
+                if (j + 2 == g.hi[s]) umma_commit(&q_empty[s]);
               }
-              umma_commit(&s_full[s]);
-              if (!other_n) umma_commit(&kv_empty[slot]);
-              if (j + 2 == g.hi[s]) umma_commit(&q_empty[s]);
+              __syncwarp();
+              FA_TR(lane == 0, 5, j - g.lo_all + 1, s * 4 + 2);
             }
           }
         }
@@ -421,6 +517,7 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           for (int t = 0; t < 2; ++t) {
             const uint32_t slot = it % Cfg::kStages;
             if (!mbar_wait(&kv_empty[slot], ((it / Cfg::kStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
+            FA_TR(true, 4, j - g.lo_all, t * 2 + 0);
             mbar_arrive_expect_tx(&kv_full[slot], Cfg::kTileBytes);
             tma_load_4d(sKV + slot * Cfg::kTileBytes, t == 0 ? &mapK : &mapV, &kv_full[slot], 0, j * kBlockN, 0, g.bh);
             ++it;
