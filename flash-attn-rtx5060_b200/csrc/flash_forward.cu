@@ -52,12 +52,18 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 constexpr int kMaxDevices = 64;
+// Each launch of the persistent kernel takes the next pair of scheduler words round-robin, so
+// that launches in flight on different streams do not share a work counter. The kernel leaves
+// its pair at zero; a pair is reused after kSchedSlots further launches on the device.
+constexpr int kSchedSlots = 64;
+constexpr size_t kDeviceWords = 4 + 2 * kSchedSlots;
 struct DeviceState {
   std::mutex mu;
   bool probed = false;
   bool is_sm100 = false;
   int num_sms = 0;
-  int* status = nullptr;  // device word
+  int* status = nullptr;  // device words: [0] status, then kSchedSlots pairs of scheduler words
+  unsigned next_sched = 0;
   bool attr_set[8] = {};
 };
 DeviceState g_dev[kMaxDevices];
@@ -78,8 +84,10 @@ int device_state(DeviceState** out) {
     s.is_sm100 = (major == 10);
     s.num_sms = sms;
     if (s.is_sm100) {
-      if ((e = cudaMalloc(&s.status, sizeof(int))) != cudaSuccess) return fail_cuda("cudaMalloc(status)", e);
-      if ((e = cudaMemset(s.status, 0, sizeof(int))) != cudaSuccess) return fail_cuda("cudaMemset(status)", e);
+      if ((e = cudaMalloc(&s.status, kDeviceWords * sizeof(int))) != cudaSuccess)
+        return fail_cuda("cudaMalloc(status)", e);
+      if ((e = cudaMemset(s.status, 0, kDeviceWords * sizeof(int))) != cudaSuccess)
+        return fail_cuda("cudaMemset(status)", e);
     }
     s.probed = true;
   }
@@ -138,7 +146,12 @@ int launch_persistent(DeviceState* s, const CUtensorMap& mq, const CUtensorMap& 
   int rc = ensure_smem_attr(s, D == 64 ? 2 : 3, fa::fwd_persistent_kernel<D>, Cfg::kSmemBytes);
   if (rc != FA_OK) return rc;
   int grid = p.num_items < s->num_sms ? p.num_items : s->num_sms;
-  fa::fwd_persistent_kernel<D><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mk, mv, p);
+  fa::FwdParams pp = p;
+  {
+    std::lock_guard<std::mutex> lk(s->mu);
+    pp.sched = s->status + 4 + 2 * (s->next_sched++ % kSchedSlots);
+  }
+  fa::fwd_persistent_kernel<D><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mk, mv, pp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail_cuda("launch fwd_persistent_kernel", e);
   return FA_OK;
@@ -282,7 +295,7 @@ int flash_forward_check(void* stream) {
   if ((e = cudaMemcpy(&host, s->status, sizeof(int), cudaMemcpyDeviceToHost)) != cudaSuccess)
     return fail_cuda("cudaMemcpy(status)", e);
   if (host != 0) {
-    cudaMemset(s->status, 0, sizeof(int));
+    cudaMemset(s->status, 0, kDeviceWords * sizeof(int));  // a give-up may leave scheduler words non-zero
     snprintf(g_err, sizeof(g_err), "a wait inside the attention kernel ran out of time (status word %d)", host);
     return FA_DEVICE_TIMEOUT;
   }

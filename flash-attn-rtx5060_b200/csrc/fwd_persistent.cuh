@@ -62,9 +62,9 @@ struct PersistentCfg {
   static constexpr int kOffAlpha = kOffKV + kStages * kTileBytes;  // float[2][128]
   static constexpr int kOffRowSum = kOffAlpha + 2 * kBlockM * 4;   // float[2][128]
   static constexpr int kOffBars = kOffRowSum + 2 * kBlockM * 4;
-  static constexpr int kNumBars = 16 + 2 * kStages;
+  static constexpr int kNumBars = 20 + 2 * kStages;
   static constexpr int kOffMisc = kOffBars + kNumBars * 8;
-  static constexpr int kSmemBytes = kOffMisc + 16;
+  static constexpr int kSmemBytes = kOffMisc + 16;  // TMEM base, abort flag, two work-item slots
   static constexpr uint32_t kTmemCols = 512;
   static constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
   // softmax threshold (in log2 units) below which a larger row max does not trigger a rescale
@@ -79,8 +79,10 @@ struct ItemGeom {
   int lo_all, hi_all;
 };
 
-// Items are ordered head-major with the longest (latest) q pair of each head first, so that a
-// causal launch starts with the most expensive items and CTAs that run together share K/V in L2.
+// Items are ordered head-major with the longest (latest) q pair of each head first. CTAs take
+// items from a global counter in that order, so CTAs that run together share K/V of a few heads
+// in L2, a causal launch starts with the most expensive items of each head, and the items handed
+// out last are the cheapest ones: the tail stays short whatever the per-item cost.
 __device__ __forceinline__ ItemGeom decode_item(int item, const FwdParams& p) {
   ItemGeom g;
   g.bh = item / p.num_q_pairs;
@@ -177,10 +179,14 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   uint64_t* l_ready = bars + 10;      // [2] softmax -> correction: final row sums in smem
   uint64_t* o_full = bars + 12;       // [2] MMA -> correction: last P.V of the item landed
   uint64_t* p_full2 = bars + 14;      // [2] softmax -> MMA: second half of P written
-  uint64_t* kv_full = bars + 16;      // [kStages] TMA -> MMA
-  uint64_t* kv_empty = bars + 16 + Cfg::kStages;  // [kStages] MMA -> TMA
+  uint64_t* item_full = bars + 16;    // [2] producer -> all roles: next work item id published
+  uint64_t* item_empty = bars + 18;   // [2] all roles -> producer: id slot read
+  uint64_t* kv_full = bars + 20;      // [kStages] TMA -> MMA
+  uint64_t* kv_empty = bars + 20 + Cfg::kStages;  // [kStages] MMA -> TMA
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* s_item = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [2]
+  constexpr uint32_t kItemReaders = 13;  // 8 softmax warps + 4 correction warps + the MMA warp
 
   if (warp == 12) {
     tmem_alloc(tmem_slot, Cfg::kTmemCols);
@@ -197,6 +203,8 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       mbar_init(&alpha_ready[s], 4);
       mbar_init(&l_ready[s], 4);
       mbar_init(&o_full[s], 1);
+      mbar_init(&item_full[s], 1);
+      mbar_init(&item_empty[s], kItemReaders);
     }
     for (int i = 0; i < Cfg::kStages; ++i) {
       mbar_init(&kv_full[i], 1);
@@ -219,6 +227,18 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   const int wl = p.window_left;
   const int wr = eff_window_right(p.causal, p.window_right);
 
+  // Every consuming warp reads the k-th work item id from slot k & 1 once the producer has
+  // published it, and releases the slot. -1 ends the walk (also after a give-up).
+  auto take_item = [&](uint32_t& n_items) -> int {
+    const uint32_t slot = n_items & 1u;
+    if (!mbar_wait_warp(&item_full[slot], (n_items >> 1) & 1u, abort_flag)) return -1;
+    const int it = s_item[slot];
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&item_empty[slot]);
+    ++n_items;
+    return it;
+  };
+
   if (warp < 8) {
     // =====================================================================================
     // softmax: stage s = warp / 4, row = tid % 128
@@ -230,8 +250,11 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     const uint32_t tS = tmem_addr(tmem_base, lane_base, s == 0 ? Cfg::kColS0 : Cfg::kColS1);
     const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2);
     uint32_t n_s = 0;  // completed s_full phases
+    uint32_t n_items = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
+    while (ok) {
+      const int item = take_item(n_items);
+      if (item < 0) break;
       const ItemGeom g = decode_item(item, p);
       const int q_r0 = s ? g.r0[1] : g.r0[0];
       const int q_r1 = s ? g.r1[1] : g.r1[0];
@@ -247,6 +270,17 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         ++n_s;
         tc_fence_after();
         FA_TR(row_l == 0, s, j - j_lo, 0);
+#ifdef FA_FAKE_SOFTMAX  // bring-up only: measures the load + tensor pipeline without the softmax work
+        if (FA_FAKE_SOFTMAX > 0) {
+          const long long t_end = clock64() + FA_FAKE_SOFTMAX;
+          while (clock64() < t_end) {}
+        }
+        sAlpha[s * kBlockM + row_l] = 1.f;
+        __syncwarp();
+        if (lane == 0) { mbar_arrive(&alpha_ready[s]); mbar_arrive(&p_full[s]); mbar_arrive(&p_full2[s]); }
+        l_run = 1.f;
+        continue;
+#endif
         uint32_t r0[32], r1[32], r2[32], r3[32];
         tmem_ld32(tS + 0, r0);
         tmem_ld32(tS + 32, r1);
@@ -338,8 +372,11 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     const int row_l = tid & 127;
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32u;
     uint32_t n_alpha[2] = {0, 0}, n_l[2] = {0, 0}, n_o[2] = {0, 0};
+    uint32_t n_items = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
+    while (ok) {
+      const int item = take_item(n_items);
+      if (item < 0) break;
       const ItemGeom g = decode_item(item, p);
       for (int j = g.lo_all; j < g.hi_all && ok; ++j) {
 #pragma unroll
@@ -421,8 +458,11 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       const uint64_t qdesc[2] = {kdesc0 + (q_addr >> 4), kdesc0 + ((q_addr + Cfg::kTileBytes) >> 4)};
       uint32_t it_base = 0;  // ring position of K tile lo_all of the current item
       uint32_t n_p[2] = {0, 0}, n_q[2] = {0, 0};
+      uint32_t n_items = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
+      while (ok) {
+        const int item = take_item(n_items);
+        if (item < 0) break;
         const ItemGeom g = decode_item(item, p);
         for (int j = g.lo_all - 1; j < g.hi_all && ok; ++j) {
 #pragma unroll
@@ -501,8 +541,22 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       // ===================================================================================
       uint32_t it = 0;
       uint32_t n_q[2] = {0, 0};
+      uint32_t n_pub = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < p.num_items && ok; item += gridDim.x) {
+      int next = (static_cast<int>(blockIdx.x) < p.num_items) ? static_cast<int>(blockIdx.x) : -1;
+      while (ok) {
+        const int item = next;
+        {  // publish the id to the other roles
+          const uint32_t slot = n_pub & 1u;
+          if (!mbar_wait(&item_empty[slot], ((n_pub >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+          s_item[slot] = item;
+          mbar_arrive(&item_full[slot]);
+          ++n_pub;
+        }
+        if (item < 0) break;
+        // claim the following item now; the value is not needed before this item's loads are issued
+        next = static_cast<int>(gridDim.x) + atomicAdd(p.sched, 1);
+        if (next >= p.num_items) next = -1;
         const ItemGeom g = decode_item(item, p);
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
@@ -533,7 +587,15 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
 
   tc_fence_before();
   __syncthreads();
-  if (tid == 0 && *abort_flag != 0) atomicExch(p.status, 1);
+  if (tid == 0) {
+    if (*abort_flag != 0) atomicExch(p.status, 1);
+    // the last CTA to finish puts the scheduler words back to zero for the next launch
+    if (atomicAdd(p.sched + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+      p.sched[0] = 0;
+      p.sched[1] = 0;
+      __threadfence();
+    }
+  }
   if (warp == 12) tmem_dealloc(tmem_base, Cfg::kTmemCols);
 }
 
