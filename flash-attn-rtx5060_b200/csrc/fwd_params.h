@@ -27,6 +27,7 @@ struct FwdParams {
   // persistent kernel only
   int num_q_pairs;   // ceil(seqlen / 256)
   int num_items;     // bh * num_q_pairs
+  int head_group;    // heads whose items are interleaved pair-major in the work-item order
   int* sched;        // device scratch, two words that are 0 between launches: [0] next work item to
                      // hand out (beyond the first gridDim.x), [1] CTAs that have finished
 };

@@ -79,14 +79,20 @@ struct ItemGeom {
   int lo_all, hi_all;
 };
 
-// Items are ordered head-major with the longest (latest) q pair of each head first. CTAs take
-// items from a global counter in that order, so CTAs that run together share K/V of a few heads
-// in L2, a causal launch starts with the most expensive items of each head, and the items handed
-// out last are the cheapest ones: the tail stays short whatever the per-item cost.
+// Work-item order. Heads are taken in groups of `head_group` (sized on the host so that the K/V of
+// a group stays in L2); inside a group the items run pair-major from the last (under a causal mask
+// the longest) q pair to the first. CTAs claim items in this order from a global counter, so CTAs
+// that run together read the same few heads, and the items handed out last are the cheapest ones
+// of the last group: the tail stays short.
 __device__ __forceinline__ ItemGeom decode_item(int item, const FwdParams& p) {
   ItemGeom g;
-  g.bh = item / p.num_q_pairs;
-  g.pair = p.num_q_pairs - 1 - (item - g.bh * p.num_q_pairs);
+  const int per_group = p.head_group * p.num_q_pairs;
+  const int grp = item / per_group;
+  const int r = item - grp * per_group;
+  const int heads_here = min(p.head_group, p.bh - grp * p.head_group);
+  const int pr = r / heads_here;
+  g.bh = grp * p.head_group + (r - pr * heads_here);
+  g.pair = p.num_q_pairs - 1 - pr;
   const int wr = eff_window_right(p.causal, p.window_right);
   g.lo_all = 0x7fffffff;
   g.hi_all = 0;
