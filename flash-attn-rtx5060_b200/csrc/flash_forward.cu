@@ -190,6 +190,73 @@ int host_pipe(HostPipe** out) {
   return FA_OK;
 }
 
+// ---- allocation-free entry point ---------------------------------------------------------
+// Scratch of flash_forward_noalloc: a fixed block in the library's own device image instead of
+// memory obtained from cudaMalloc. kNoAllocSlots slots of four ints each:
+//   word 0 status (set non-zero when a bounded wait inside the kernel gave up),
+//   words 2-3 the persistent kernel's work counter and finished-CTA counter.
+// 256 bytes per GPU that loads the library, held until the process exits.
+constexpr int kNoAllocSlots = 16;
+static __device__ __align__(256) int g_noalloc_scratch[kNoAllocSlots * 4];
+
+// Host-side record of the set-up done once per device for the allocation-free path. In host code
+// `g_noalloc_scratch` is only a handle for the runtime; the device address the kernel needs comes
+// from cudaGetSymbolAddress, asked with that device current.
+struct NoAllocState {
+  std::mutex mu;
+  bool ready = false;
+  int num_sms = 0;
+  int* scratch = nullptr;  // device address of g_noalloc_scratch on this device
+  bool attr_set[2] = {};
+};
+NoAllocState g_noalloc[kMaxDevices];
+
+int noalloc_state(NoAllocState** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail_cuda("cudaGetDevice", e);
+  if (dev < 0 || dev >= kMaxDevices) return fail(FA_UNSUPPORTED, "device ordinal out of range");
+  NoAllocState& s = g_noalloc[dev];
+  std::lock_guard<std::mutex> lk(s.mu);
+  if (!s.ready) {
+    int major = 0, sms = 0;
+    if ((e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess)
+      return fail_cuda("cudaDeviceGetAttribute", e);
+    if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess)
+      return fail_cuda("cudaDeviceGetAttribute", e);
+    if (major != 10) return fail(FA_UNSUPPORTED, "this library runs on compute capability 10.x (B200) only");
+    void* ptr = nullptr;
+    if ((e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch)) != cudaSuccess)
+      return fail_cuda("cudaGetSymbolAddress(g_noalloc_scratch)", e);
+    s.scratch = static_cast<int*>(ptr);
+    s.num_sms = sms;
+    s.ready = true;
+  }
+  *out = &s;
+  return FA_OK;
+}
+
+template <int D>
+int launch_persistent_noalloc(NoAllocState* s, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                              const fa::FwdParams& p, cudaStream_t st) {
+  using Cfg = fa::PersistentCfg<D>;
+  {
+    std::lock_guard<std::mutex> lk(s->mu);
+    bool& done = s->attr_set[D == 64 ? 0 : 1];
+    if (!done) {
+      cudaError_t e = cudaFuncSetAttribute(fa::fwd_persistent_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           Cfg::kSmemBytes);
+      if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(MaxDynamicSharedMemorySize)", e);
+      done = true;
+    }
+  }
+  const int grid = p.num_items < s->num_sms ? p.num_items : s->num_sms;
+  fa::fwd_persistent_kernel<D><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mk, mv, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail_cuda("launch fwd_persistent_kernel", e);
+  return FA_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -398,6 +465,84 @@ int flash_forward_host(const void* q_host, const void* k_host, const void* v_hos
   int rc_run = flash_forward_check(hp->run);
   if ((e = cudaStreamSynchronize(hp->down)) != cudaSuccess && rc == FA_OK) rc = fail_cuda("cudaStreamSynchronize", e);
   return rc != FA_OK ? rc : rc_run;
+}
+
+int flash_forward_noalloc(const void* q, const void* k, const void* v, void* o, int batch, int heads, int seqlen,
+                          int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,
+                          void* stream, int slot, int wait) {
+  if (!q || !k || !v || !o) return fail(FA_INVALID_ARG, "null tensor pointer");
+  if (batch <= 0 || heads <= 0 || seqlen <= 0) return fail(FA_INVALID_ARG, "batch, heads and seqlen must be positive");
+  if (head_dim != 64 && head_dim != 128) return fail(FA_UNSUPPORTED, "head_dim must be 64 or 128");
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(o)) & 15)
+    return fail(FA_INVALID_ARG, "tensor pointers must be 16-byte aligned");
+  if (slot < 0 || slot >= kNoAllocSlots) {
+    snprintf(g_err, sizeof(g_err),
+             "scratch slot %d is outside the %d slots (256 bytes) that the library's static device scratch holds",
+             slot, kNoAllocSlots);
+    return FA_INVALID_ARG;
+  }
+  if (!(softmax_scale == softmax_scale)) return fail(FA_INVALID_ARG, "softmax_scale is NaN");
+  const long long bh_ll = (long long)batch * heads;
+  const int pairs = (seqlen + 2 * fa::kBlockM - 1) / (2 * fa::kBlockM);
+  // the work counter in the scratch is a 32-bit int to which the kernel adds the grid size
+  if (bh_ll > 0x7fffffffLL || bh_ll * pairs > 0x7fffffffLL - 65536) {
+    snprintf(g_err, sizeof(g_err),
+             "batch*heads*ceil(seqlen/256) = %lld work items do not fit the 32-bit work counter of the static scratch",
+             bh_ll * pairs);
+    return FA_INVALID_ARG;
+  }
+
+  NoAllocState* s = nullptr;
+  int rc = noalloc_state(&s);
+  if (rc != FA_OK) return rc;
+  if (softmax_scale <= 0.f) softmax_scale = 1.0f / sqrtf((float)head_dim);
+  const int bh = (int)bh_ll;
+  int* words = s->scratch + slot * 4;
+
+  fa::FwdParams p;
+  memset(&p, 0, sizeof(p));
+  p.O = static_cast<__half*>(o);
+  p.seqlen = seqlen;
+  p.bh = bh;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.causal = is_causal ? 1 : 0;
+  p.window_left = window_left < 0 ? -1 : window_left;
+  p.window_right = window_right < 0 ? -1 : window_right;
+  p.status = words;
+  p.sched = words + 2;
+  p.num_q_pairs = pairs;
+  p.num_items = bh * pairs;
+  {
+    const double head_bytes = 4.0 * seqlen * head_dim;
+    int grp = (int)(96.0 * 1024 * 1024 / head_bytes);
+    p.head_group = grp < 1 ? 1 : (grp > 16 ? 16 : grp);
+    if (!p.causal && p.window_left < 0 && p.window_right < 0) p.head_group = 1;
+    if (p.head_group > bh) p.head_group = bh;
+  }
+
+  CUtensorMap mq, mk, mv;
+  if ((rc = make_map(&mq, q, bh, seqlen, head_dim, fa::kBlockM)) != FA_OK) return rc;
+  if ((rc = make_map(&mk, k, bh, seqlen, head_dim, fa::kBlockN)) != FA_OK) return rc;
+  if ((rc = make_map(&mv, v, bh, seqlen, head_dim, fa::kBlockN)) != FA_OK) return rc;
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The slot keeps whatever the previous call left; status and both counters must start at zero.
+  cudaError_t e = cudaMemsetAsync(words, 0, 4 * sizeof(int), st);
+  if (e != cudaSuccess) return fail_cuda("cudaMemsetAsync(scratch slot)", e);
+  rc = head_dim == 64 ? launch_persistent_noalloc<64>(s, mq, mk, mv, p, st)
+                      : launch_persistent_noalloc<128>(s, mq, mk, mv, p, st);
+  if (rc != FA_OK || !wait) return rc;
+
+  if ((e = cudaStreamSynchronize(st)) != cudaSuccess) return fail_cuda("cudaStreamSynchronize", e);
+  int host = 0;
+  if ((e = cudaMemcpy(&host, words, sizeof(int), cudaMemcpyDeviceToHost)) != cudaSuccess)
+    return fail_cuda("cudaMemcpy(status)", e);
+  if (host != 0) {
+    snprintf(g_err, sizeof(g_err), "a wait inside the attention kernel ran out of time (status word %d)", host);
+    return FA_DEVICE_TIMEOUT;
+  }
+  return FA_OK;
 }
 
 int flash_forward_shutdown(void) {

@@ -104,6 +104,34 @@ double flash_forward_flops(int batch, int heads, int seqlen, int head_dim, int i
 int flash_forward_kv_range(int seqlen, int is_causal, int window_left, int window_right, int row_begin,
                            int row_end, int* tile_begin, int* tile_end, int* masked_tiles);
 
+/* Attention forward for callers that must not allocate device memory. No counterpart in the
+ * reference. flash_forward() above obtains its few words of device scratch (status word, work
+ * counters) from cudaMalloc on the first call per device. Some hosts cannot afford that call:
+ * a serving process whose device memory is handed out entirely by its own pool, where a stray
+ * cudaMalloc can fail or fragment the pool; a latency-critical loop, because cudaMalloc
+ * synchronises the whole device; a plug-in that runs under an allocator hook which forbids
+ * raw allocations. For them this entry point runs the same persistent kernel with its scratch
+ * in a fixed 256-byte array that is part of the library's device image (every GPU that loads
+ * the library holds those 256 bytes until the process exits). It calls no cudaMalloc, cudaFree
+ * or other allocating routine.
+ *
+ *   slot  which of the 16 four-word scratch slots this call uses, 0..15. Anything else is
+ *         rejected with FA_INVALID_ARG; so is a problem whose work-item count
+ *         batch*heads*ceil(seqlen/256) does not fit the slot's 32-bit work counter.
+ *   wait  0: return once the work is enqueued on `stream` (a device-side time-out then goes
+ *         unreported); non-zero: block until the kernel has finished and return
+ *         FA_DEVICE_TIMEOUT if its status word was set.
+ *
+ * All other arguments as for flash_forward(). A slot keeps the contents the last call left in it;
+ * every call first clears its slot on `stream`. Calls that use the same slot must not overlap on
+ * the GPU (they would share one work counter and race); calls on different slots may.
+ * The first call on a device performs a one-time set-up (looks up the scratch array's device
+ * address, sets the kernel's shared-memory attribute); make that first call before any stream
+ * capture begins. */
+int flash_forward_noalloc(const void* q, const void* k, const void* v, void* o, int batch, int heads, int seqlen,
+                          int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,
+                          void* stream, int slot, int wait);
+
 /* Frees the per-device status words this library allocated. Optional. */
 int flash_forward_shutdown(void);
 

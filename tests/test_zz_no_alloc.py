@@ -1,0 +1,79 @@
+"""GPU test of flash_forward_noalloc, the entry point for callers that must not allocate device
+memory (a process whose memory pool owns the whole GPU, a latency-critical loop that cannot take
+cudaMalloc's device-wide synchronisation, a plug-in under an allocator hook). It runs the same
+persistent kernel as flash_forward, with the kernel's scratch words in a fixed array inside the
+library instead of memory from cudaMalloc.
+
+The file name keeps it last in collection order, so a run that stops at the first failure has
+already run every other test. The test works alone in a fresh process and after the other tests."""
+import ctypes
+
+import numpy as np
+import pytest
+
+from conftest import make_inputs
+
+pytestmark = pytest.mark.gpu
+
+
+def call_noalloc(pkg, q, k, v, o, B, H, N, d, causal, wl, wr, slot, wait=1):
+    import torch
+
+    stream = torch.cuda.current_stream().cuda_stream
+    return pkg.lib().flash_forward_noalloc(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), B, H, N, d, 0.0,
+                                           int(causal), wl, wr, stream, slot, wait)
+
+
+@pytest.mark.parametrize("B,H,N,d,causal,wl", [(2, 6, 1024, 128, True, -1), (1, 5, 777, 64, True, 200)])
+def test_noalloc_matches_flash_forward_twice_in_a_row(pkg, ob, B, H, N, d, causal, wl):
+    import torch
+
+    q, k, v = make_inputs(41, B, H, N, d)
+    tq, tk, tv = (torch.from_numpy(a).cuda() for a in (q, k, v))
+    want = pkg.attention_forward(tq, tk, tv, causal=causal, window_left=wl)
+    pkg.check(torch.cuda.current_stream().cuda_stream)
+    want = want.cpu().numpy()
+    oracle = ob.attention(q, k, v, causal=causal, window_left=wl, window_right=-1)
+    for attempt in range(2):  # the second call finds the slot as the first one left it
+        out = torch.full_like(tq, float("nan"))
+        rc = call_noalloc(pkg, tq, tk, tv, out, B, H, N, d, causal, wl, -1, slot=3)
+        assert rc == pkg.FA_OK, pkg.lib().flash_forward_last_error()
+        got = out.cpu().numpy()
+        mx, mean, nans = ob.abs_error(got, want)
+        assert nans == 0 and mx <= 2e-3 and mean <= 2e-4, (attempt, mx, mean, nans)
+        mx, mean, nans = ob.abs_error(got, oracle)
+        assert nans == 0 and mx <= 2e-3 and mean <= 2e-4, (attempt, mx, mean, nans)
+
+
+def test_noalloc_async_then_other_slot(pkg, ob):
+    import torch
+
+    B, H, N, d = 1, 4, 512, 128
+    q, k, v = make_inputs(43, B, H, N, d)
+    tq, tk, tv = (torch.from_numpy(a).cuda() for a in (q, k, v))
+    a = torch.empty_like(tq)
+    b = torch.empty_like(tq)
+    assert call_noalloc(pkg, tq, tk, tv, a, B, H, N, d, False, -1, -1, slot=0, wait=0) == pkg.FA_OK
+    assert call_noalloc(pkg, tq, tk, tv, b, B, H, N, d, False, -1, -1, slot=15, wait=1) == pkg.FA_OK
+    torch.cuda.synchronize()
+    assert torch.equal(a, b)
+    want = ob.attention(q, k, v)
+    mx, mean, nans = ob.abs_error(a.cpu().numpy(), want)
+    assert nans == 0 and mx <= 2e-3 and mean <= 2e-4
+
+
+def test_noalloc_rejects_what_the_scratch_cannot_hold(pkg):
+    import torch
+
+    t = torch.zeros((1, 1, 128, 64), dtype=torch.float16, device="cuda")
+    for slot in (-1, 16, 1000):
+        rc = call_noalloc(pkg, t, t, t, t, 1, 1, 128, 64, False, -1, -1, slot=slot)
+        assert rc == pkg.FA_INVALID_ARG
+        assert b"slot" in pkg.lib().flash_forward_last_error()
+    # more work items than the slot's 32-bit counter can number
+    rc = pkg.lib().flash_forward_noalloc(t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), 1 << 15, 1 << 15,
+                                         1024, 64, 0.0, 0, -1, -1, None, 0, 1)
+    assert rc == pkg.FA_INVALID_ARG
+    assert b"work items" in pkg.lib().flash_forward_last_error()
+    assert pkg.lib().flash_forward_noalloc(t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), 1, 1, 128, 96, 0.0,
+                                           0, -1, -1, None, 0, 1) == pkg.FA_UNSUPPORTED
