@@ -24,6 +24,7 @@ STATUS_NAMES = {0: "FA_OK", 1: "FA_INVALID_ARG", 2: "FA_UNSUPPORTED", 3: "FA_CUD
 EXPORTS = (
     "flash_forward",
     "flash_forward_ex",
+    "flash_forward_alibi",
     "flash_forward_host",
     "flash_forward_host_workspace_bytes",
     "flash_forward_check",
@@ -55,6 +56,8 @@ def lib():
     vp, i, f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
     L.flash_forward.argtypes = [vp, vp, vp, vp, i, i, i, i, f, i, i, i, vp]
     L.flash_forward.restype = i
+    L.flash_forward_alibi.argtypes = [vp, vp, vp, vp, i, i, i, i, f, i, i, i, vp, vp]
+    L.flash_forward_alibi.restype = i
     L.flash_forward_ex.argtypes = [vp, vp, vp, vp, i, i, i, i, f, i, i, i, vp, i, i, vp]
     L.flash_forward_ex.restype = i
     L.flash_forward_host.argtypes = [vp, vp, vp, vp, i, i, i, i, f, i, i, i, vp, ctypes.c_size_t, i]
@@ -143,7 +146,7 @@ def run_flash_attention(B, N, S, d, Q, K, V, O, L=None, M=None, Is_dropout=False
 
 
 def attention_forward(q, k, v, causal=False, window_left=-1, window_right=-1, softmax_scale=0.0, out=None, kernel=0,
-                      variant=0):
+                      variant=0, alibi_slopes=None):
     """Convenience wrapper for torch CUDA tensors of shape [B, H, N, d], fp16, contiguous.
 
     torch is used for device memory and the current stream only; the computation is the library's.
@@ -157,6 +160,14 @@ def attention_forward(q, k, v, causal=False, window_left=-1, window_right=-1, so
         out = torch.empty_like(q)
     stream = torch.cuda.current_stream(q.device).cuda_stream
     with torch.cuda.device(q.device):
-        flash_forward(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, H, N, d, softmax_scale, causal,
-                      window_left, window_right, stream, kernel, variant)
+        if alibi_slopes is not None:  # float32 CUDA tensor with one slope per head
+            assert alibi_slopes.is_cuda and alibi_slopes.dtype == torch.float32 and alibi_slopes.numel() == H
+            rc = lib().flash_forward_alibi(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, H, N, d,
+                                           softmax_scale, int(bool(causal)), window_left, window_right,
+                                           alibi_slopes.data_ptr(), stream)
+            if rc != FA_OK:
+                _raise(rc)
+        else:
+            flash_forward(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, H, N, d, softmax_scale, causal,
+                          window_left, window_right, stream, kernel, variant)
     return out

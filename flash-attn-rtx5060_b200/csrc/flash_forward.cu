@@ -144,7 +144,9 @@ template <int D>
 int launch_persistent(DeviceState* s, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                       const fa::FwdParams& p, cudaStream_t st) {
   using Cfg = fa::PersistentCfg<D>;
-  int rc = ensure_smem_attr(s, D == 64 ? 2 : 3, fa::fwd_persistent_kernel<D>, Cfg::kSmemBytes);
+  const bool alibi = p.alibi_slopes != nullptr;
+  int rc = alibi ? ensure_smem_attr(s, D == 64 ? 4 : 5, fa::fwd_persistent_kernel<D, true>, Cfg::kSmemBytes)
+                 : ensure_smem_attr(s, D == 64 ? 2 : 3, fa::fwd_persistent_kernel<D, false>, Cfg::kSmemBytes);
   if (rc != FA_OK) return rc;
   int grid = p.num_items < s->num_sms ? p.num_items : s->num_sms;
   fa::FwdParams pp = p;
@@ -152,7 +154,8 @@ int launch_persistent(DeviceState* s, const CUtensorMap& mq, const CUtensorMap& 
     std::lock_guard<std::mutex> lk(s->mu);
     pp.sched = s->status + 4 + 2 * (s->next_sched++ % kSchedSlots);
   }
-  fa::fwd_persistent_kernel<D><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mk, mv, pp);
+  if (alibi) fa::fwd_persistent_kernel<D, true><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mk, mv, pp);
+  else fa::fwd_persistent_kernel<D, false><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mk, mv, pp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail_cuda("launch fwd_persistent_kernel", e);
   return FA_OK;
@@ -244,14 +247,14 @@ int launch_persistent_noalloc(NoAllocState* s, const CUtensorMap& mq, const CUte
     std::lock_guard<std::mutex> lk(s->mu);
     bool& done = s->attr_set[D == 64 ? 0 : 1];
     if (!done) {
-      cudaError_t e = cudaFuncSetAttribute(fa::fwd_persistent_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      cudaError_t e = cudaFuncSetAttribute(fa::fwd_persistent_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            Cfg::kSmemBytes);
       if (e != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(MaxDynamicSharedMemorySize)", e);
       done = true;
     }
   }
   const int grid = p.num_items < s->num_sms ? p.num_items : s->num_sms;
-  fa::fwd_persistent_kernel<D><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mk, mv, p);
+  fa::fwd_persistent_kernel<D, false><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mk, mv, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail_cuda("launch fwd_persistent_kernel", e);
   return FA_OK;
@@ -295,10 +298,11 @@ int flash_forward_kv_range(int seqlen, int is_causal, int window_left, int windo
   return FA_OK;
 }
 
-int flash_forward_ex(const void* q, const void* k, const void* v, void* o, int batch, int heads, int seqlen,
-                     int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,
-                     void* stream, int kernel, int variant, float* dbg) {
+static int forward_impl(const void* q, const void* k, const void* v, void* o, int batch, int heads, int seqlen,
+                        int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,
+                        const float* alibi_slopes, void* stream, int kernel, int variant, float* dbg) {
   if (!q || !k || !v || !o) return fail(FA_INVALID_ARG, "null tensor pointer");
+  if (alibi_slopes && kernel == 1) return fail(FA_UNSUPPORTED, "the serial kernel has no ALiBi path");
   if (batch <= 0 || heads <= 0 || seqlen <= 0) return fail(FA_INVALID_ARG, "batch, heads and seqlen must be positive");
   if (head_dim != 64 && head_dim != 128) return fail(FA_UNSUPPORTED, "head_dim must be 64 or 128");
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
@@ -328,6 +332,8 @@ int flash_forward_ex(const void* q, const void* k, const void* v, void* o, int b
   p.status = s->status;
   p.dbg = dbg;
   p.variant = variant;
+  p.alibi_slopes = alibi_slopes;
+  p.heads = heads;
   p.num_q_pairs = (seqlen + 2 * fa::kBlockM - 1) / (2 * fa::kBlockM);
   if ((long long)bh * p.num_q_pairs > 0x7fffffffLL) return fail(FA_INVALID_ARG, "too many work items");
   p.num_items = bh * p.num_q_pairs;
@@ -358,11 +364,26 @@ int flash_forward_ex(const void* q, const void* k, const void* v, void* o, int b
   return head_dim == 64 ? launch_persistent<64>(s, mq, mk, mv, p, st) : launch_persistent<128>(s, mq, mk, mv, p, st);
 }
 
+int flash_forward_ex(const void* q, const void* k, const void* v, void* o, int batch, int heads, int seqlen,
+                     int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,
+                     void* stream, int kernel, int variant, float* dbg) {
+  return forward_impl(q, k, v, o, batch, heads, seqlen, head_dim, softmax_scale, is_causal, window_left, window_right,
+                      nullptr, stream, kernel, variant, dbg);
+}
+
 int flash_forward(const void* q, const void* k, const void* v, void* o, int batch, int heads, int seqlen,
                   int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,
                   void* stream) {
-  return flash_forward_ex(q, k, v, o, batch, heads, seqlen, head_dim, softmax_scale, is_causal, window_left,
-                          window_right, stream, 0, 0, nullptr);
+  return forward_impl(q, k, v, o, batch, heads, seqlen, head_dim, softmax_scale, is_causal, window_left, window_right,
+                      nullptr, stream, 0, 0, nullptr);
+}
+
+int flash_forward_alibi(const void* q, const void* k, const void* v, void* o, int batch, int heads, int seqlen,
+                        int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,
+                        const float* alibi_slopes, void* stream) {
+  if (!alibi_slopes) return fail(FA_INVALID_ARG, "alibi_slopes is null");
+  return forward_impl(q, k, v, o, batch, heads, seqlen, head_dim, softmax_scale, is_causal, window_left, window_right,
+                      alibi_slopes, stream, 0, 0, nullptr);
 }
 
 int flash_forward_check(void* stream) {
@@ -387,9 +408,9 @@ int flash_forward_check(void* stream) {
 int run_flash_attention_c(int B, int N, int S, int d, void* Q, void* K, void* V, void* O, void* L, void* M,
                           int Is_dropout, int Is_causal, int Is_local, int Has_alibi, int window_size,
                           float* alibi_slopes, float dropout_prob, void* states) {
-  (void)L; (void)M; (void)alibi_slopes; (void)dropout_prob; (void)states;
+  (void)L; (void)M; (void)dropout_prob; (void)states;
   if (Is_dropout) return fail(FA_UNSUPPORTED, "dropout is outside this library's path");
-  if (Has_alibi) return fail(FA_UNSUPPORTED, "ALiBi is outside this library's path");
+  if (Has_alibi && !alibi_slopes) return fail(FA_INVALID_ARG, "Has_alibi needs alibi_slopes");
   if (Is_local && window_size < 0) return fail(FA_INVALID_ARG, "Is_local needs window_size >= 0");
   const int wl = Is_local ? window_size : -1;
   const int wr = Is_local ? window_size : -1;
@@ -398,7 +419,8 @@ int run_flash_attention_c(int B, int N, int S, int d, void* Q, void* K, void* V,
   if ((e = cudaEventCreate(&t0)) != cudaSuccess) return fail_cuda("cudaEventCreate", e);
   if ((e = cudaEventCreate(&t1)) != cudaSuccess) { cudaEventDestroy(t0); return fail_cuda("cudaEventCreate", e); }
   cudaEventRecord(t0, 0);
-  int rc = flash_forward(Q, K, V, O, B, N, S, d, 0.f, Is_causal, wl, wr, nullptr);
+  int rc = forward_impl(Q, K, V, O, B, N, S, d, 0.f, Is_causal, wl, wr, Has_alibi ? alibi_slopes : nullptr, nullptr, 0,
+                        0, nullptr);
   cudaEventRecord(t1, 0);
   if (rc == FA_OK) rc = flash_forward_check(nullptr);
   float ms = 0.f;

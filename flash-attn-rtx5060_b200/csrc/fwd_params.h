@@ -28,6 +28,9 @@ struct FwdParams {
   int num_q_pairs;   // ceil(seqlen / 256)
   int num_items;     // bh * num_q_pairs
   int head_group;    // heads whose items are interleaved pair-major in the work-item order
+  const float* alibi_slopes;  // optional, one slope per head (device); the score of (i, j) gets
+                              // -slope * |i - j| after scaling, as the reference does (src/mask.h:21-26)
+  int heads;         // heads per batch entry (indexes alibi_slopes)
   int* sched;        // device scratch, two words that are 0 between launches: [0] next work item to
                      // hand out (beyond the first gridDim.x), [1] CTAs that have finished
 };

@@ -156,7 +156,7 @@ __device__ __forceinline__ void exp_half_tile(const float* sc, uint64_t scale2, 
   }
 }
 
-template <int D>
+template <int D, bool kAlibi>
 __global__ void __launch_bounds__(512, 1)
 fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                       const __grid_constant__ CUtensorMap mapV, const FwdParams p) {
@@ -254,7 +254,10 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     const int row_l = tid & 127;
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32u;
     const uint32_t tS = tmem_addr(tmem_base, lane_base, s == 0 ? Cfg::kColS0 : Cfg::kColS1);
-    const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2);
+    // With ALiBi the scores are moved to the biased log2 domain right after the TMEM load, and
+    // everything downstream works with a unit scale.
+    const float sl2 = kAlibi ? 1.f : p.scale_log2;
+    const uint64_t scale2 = f2_pack(sl2, sl2);
     uint32_t n_s = 0;  // completed s_full phases
     uint32_t n_items = 0;
     bool ok = true;
@@ -268,6 +271,8 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       const int j_hi = s ? g.hi[1] : g.hi[0];
       if (q_r1 < q_r0) continue;
       const int row = q_r0 + row_l;
+      float slope_l2 = 0.f;
+      if (kAlibi) slope_l2 = p.alibi_slopes[g.bh % p.heads] * 1.4426950408889634f;
       float m_run = -INFINITY;  // true running max of the raw scores
       float m_used = 0.f;       // max the exponentials are currently taken against
       float l_run = 0.f;
@@ -307,6 +312,12 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           sc[96 + i] = __uint_as_float(r3[i]);
         }
         const int kv0 = j * kBlockN;
+        if (kAlibi) {  // s * scale - slope * |i - j|, in log2 units (reference: src/mask.h:21-26, src/main.cu:200-207)
+          const float rel = static_cast<float>(row - kv0);
+#pragma unroll
+          for (int c = 0; c < kBlockN; ++c)
+            sc[c] = fmaf(sc[c], p.scale_log2, -slope_l2 * fabsf(rel - static_cast<float>(c)));
+        }
         const bool masked = kv_tile_needs_mask(kv0, q_r0, q_r1, wl, wr, N);
         if (masked) {
           const int c_lo = (wl >= 0) ? row - wl - kv0 : -1;
@@ -330,8 +341,8 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         float alpha = 1.f;
         if (m_run == -INFINITY) {
           m_used = (m_new == -INFINITY) ? 0.f : m_new;
-        } else if ((m_new - m_used) * p.scale_log2 > Cfg::kLazyLog2) {
-          alpha = ex2_approx((m_used - m_new) * p.scale_log2);
+        } else if ((m_new - m_used) * sl2 > Cfg::kLazyLog2) {
+          alpha = ex2_approx((m_used - m_new) * sl2);
           m_used = m_new;
         }
         m_run = m_new;
@@ -340,7 +351,7 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         if (lane == 0) mbar_arrive(&alpha_ready[s]);
         FA_TR(row_l == 0, s, j - j_lo, 2);
 
-        const float neg_ms = -m_used * p.scale_log2;
+        const float neg_ms = -m_used * sl2;
         const uint64_t negms2 = f2_pack(neg_ms, neg_ms);
         uint64_t lsum_a = 0ull, lsum_b = 0ull;
         uint32_t pk0[32], pk1[32];

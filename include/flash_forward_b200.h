@@ -20,7 +20,7 @@ extern "C" {
 enum {
   FA_OK = 0,
   FA_INVALID_ARG = 1,    /* null or misaligned pointer, non-positive size */
-  FA_UNSUPPORTED = 2,    /* head_dim not 64/128, dropout, ALiBi, device is not sm_100 */
+  FA_UNSUPPORTED = 2,    /* head_dim not 64/128, dropout, device is not sm_100 */
   FA_CUDA_ERROR = 3,     /* a CUDA runtime/driver call failed; see flash_forward_last_error() */
   FA_DEVICE_TIMEOUT = 4  /* a bounded wait inside the kernel gave up (status word set) */
 };
@@ -46,6 +46,14 @@ enum {
 int flash_forward(const void* q, const void* k, const void* v, void* o, int batch, int heads, int seqlen,
                   int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,
                   void* stream);
+
+/* The same forward with the reference's ALiBi bias: the scaled score of (query i, key j) of head h
+ * gets -alibi_slopes[h] * |i - j| before the masks (src/mask.h:21-26,49-54,71-83 on the GPU side,
+ * src/main.cu:200-207 on the CPU side; the reference's own slopes are negative, src/main.cu:41).
+ * alibi_slopes: `heads` floats in device memory. All other arguments as for flash_forward(). */
+int flash_forward_alibi(const void* q, const void* k, const void* v, void* o, int batch, int heads, int seqlen,
+                        int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,
+                        const float* alibi_slopes, void* stream);
 
 /* Same operation with an explicit kernel choice, for tests and bring-up:
  *   kernel  0 = default (warp-specialised persistent kernel), 1 = serial one-tile-per-CTA kernel
@@ -81,7 +89,8 @@ int flash_forward_check(void* stream);
  *   Is_local  -> window_left = window_right = window_size (symmetric, :640-641; mask.h:55)
  *   Is_causal -> window_right = 0 (both masks apply when both flags are set, mask.h:15,:43)
  *   L, M      -> ignored (the reference never reads them)
- *   Is_dropout / Has_alibi -> FA_UNSUPPORTED (outside this library's path)
+ *   Has_alibi -> alibi_slopes (device, one float per head) is applied as in flash_forward_alibi()
+ *   Is_dropout -> FA_UNSUPPORTED (outside this library's path)
  * Unlike the reference it runs on the current device and returns a status instead of exiting. */
 int run_flash_attention_c(int B, int N, int S, int d, void* Q, void* K, void* V, void* O, void* L, void* M,
                           int Is_dropout, int Is_causal, int Is_local, int Has_alibi, int window_size,

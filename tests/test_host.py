@@ -51,7 +51,9 @@ def test_argument_errors_are_status_codes(pkg):
     assert L.flash_forward_ex(p, p, p, p, 1, 1, 128, 64, 0.0, 0, -1, -1, None, 7, 0, None) == pkg.FA_INVALID_ARG
     # the reference's flags that are outside this path
     assert L.run_flash_attention_c(1, 1, 128, 64, p, p, p, p, None, None, 1, 0, 0, 0, 0, None, 0.5, None) == pkg.FA_UNSUPPORTED
-    assert L.run_flash_attention_c(1, 1, 128, 64, p, p, p, p, None, None, 0, 0, 0, 1, 0, None, 0.0, None) == pkg.FA_UNSUPPORTED
+    # ALiBi without slopes is a caller error
+    assert L.run_flash_attention_c(1, 1, 128, 64, p, p, p, p, None, None, 0, 0, 0, 1, 0, None, 0.0, None) == pkg.FA_INVALID_ARG
+    assert L.flash_forward_alibi(p, p, p, p, 1, 1, 128, 64, 0.0, 0, -1, -1, None, None) == pkg.FA_INVALID_ARG
     with pytest.raises(pkg.FlashForwardError):
         pkg.run_flash_attention(1, 1, 128, 64, 0x1000, 0x1000, 0x1000, 0x1000, Is_dropout=True)
 

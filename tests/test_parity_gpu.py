@@ -31,6 +31,42 @@ def assert_close(ob, got, want, max_abs=MAX_ABS, mean_abs=MEAN_ABS):
     return mx, mean
 
 
+def test_golden_alibi(pkg, ob):
+    """The reference's ALiBi bias (src/mask.h:21-26, src/main.cu:200-207) against the golden vector made by its CPU
+    function, through both the native entry point and the reference's positional one."""
+    import torch
+
+    z = np.load(os.path.join(GOLDEN_DIR, "case_n256d64_causal_alibi.npz"))
+    q, k, v = (z[n].view(np.float16) for n in ("q", "k", "v"))
+    want = z["out"].view(np.float16)
+    B, H, N, d = q.shape
+    tq, tk, tv = (torch.from_numpy(np.ascontiguousarray(a)).cuda() for a in (q, k, v))
+    slopes = torch.from_numpy(z["slopes"]).cuda()
+    out = pkg.attention_forward(tq, tk, tv, causal=True, alibi_slopes=slopes)
+    pkg.check(torch.cuda.current_stream().cuda_stream)
+    assert_close(ob, out.cpu().numpy(), want)
+    out2 = torch.empty_like(tq)
+    torch.cuda.synchronize()
+    pkg.run_flash_attention(B, H, N, d, tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), out2.data_ptr(), None, None,
+                            False, True, False, True, 0, slopes.data_ptr())
+    assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("N,d,causal,w", [(700, 128, False, -1), (1000, 64, True, 130), (512, 128, False, 64)])
+def test_alibi_against_oracle(pkg, ob, N, d, causal, w):
+    import torch
+
+    H = 3
+    q, k, v = make_inputs(77 + N, 2, H, N, d)
+    slopes = np.array([-(2.0 ** (-8.0 / H * (i + 1))) for i in range(H)], dtype=np.float32)  # src/main.cu:41
+    want = ob.attention(q, k, v, causal=causal, window_left=w, window_right=w, alibi_slopes=slopes)
+    tq, tk, tv = (torch.from_numpy(a).cuda() for a in (q, k, v))
+    out = pkg.attention_forward(tq, tk, tv, causal=causal, window_left=w, window_right=w,
+                                alibi_slopes=torch.from_numpy(slopes).cuda())
+    pkg.check(torch.cuda.current_stream().cuda_stream)
+    assert_close(ob, out.cpu().numpy(), want, max_abs=4e-3)  # the positive bias concentrates mass: |o| passes 4
+
+
 @pytest.mark.parametrize("kernel", [0, 1])
 @pytest.mark.parametrize("fname", [f for f in golden_cases() if "alibi" not in f])
 def test_golden_vectors(pkg, ob, fname, kernel):
