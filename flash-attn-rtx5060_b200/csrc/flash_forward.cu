@@ -17,6 +17,7 @@
 
 #include "../../include/flash_forward_b200.h"
 #include "fwd_params.h"
+#include "fwd_pair.cuh"
 #include "fwd_persistent.cuh"
 #include "fwd_serial.cuh"
 
@@ -100,12 +101,13 @@ int device_state(DeviceState** out) {
 // panel, head}. One box = 128 rows x all panels of one head, landing in shared memory as
 // [panel][row][64] with the 128-byte swizzle a UMMA descriptor expects. Out-of-range rows of
 // a ragged last tile read as zero.
-int make_map(CUtensorMap* map, const void* base, int bh, int seqlen, int head_dim, int box_rows) {
+int make_map(CUtensorMap* map, const void* base, int bh, int seqlen, int head_dim, int box_rows, int box_panels = 0) {
+  if (box_panels <= 0) box_panels = head_dim / 64;
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return fail(FA_CUDA_ERROR, "cuTensorMapEncodeTiled entry point not available");
   cuuint64_t dims[4] = {64, (cuuint64_t)seqlen, (cuuint64_t)(head_dim / 64), (cuuint64_t)bh};
   cuuint64_t strides[3] = {(cuuint64_t)head_dim * 2, 128, (cuuint64_t)seqlen * head_dim * 2};
-  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, (cuuint32_t)(head_dim / 64), 1};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, (cuuint32_t)box_panels, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -137,6 +139,29 @@ int launch_serial(DeviceState* s, const CUtensorMap& mq, const CUtensorMap& mk, 
   fa::fwd_serial_kernel<D><<<grid, 128, Cfg::kSmemBytes, st>>>(mq, mk, mv, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail_cuda("launch fwd_serial_kernel", e);
+  return FA_OK;
+}
+
+// CTA-pair kernel (head_dim 128): clusters of two CTAs, static serpentine work assignment.
+int launch_pair(DeviceState* s, const void* q, const void* k, const void* v, fa::FwdParams p, cudaStream_t st) {
+  using Cfg = fa::PairCfg;
+  const bool alibi = p.alibi_slopes != nullptr;
+  int rc = alibi ? ensure_smem_attr(s, 7, fa::fwd_pair_kernel<true>, Cfg::kSmemBytes)
+                 : ensure_smem_attr(s, 6, fa::fwd_pair_kernel<false>, Cfg::kSmemBytes);
+  if (rc != FA_OK) return rc;
+  const int quads = (p.seqlen + 4 * fa::kBlockM - 1) / (4 * fa::kBlockM);
+  p.num_q_pairs = quads;  // the pair kernel counts items in quads of q tiles
+  p.num_items = p.bh * quads;
+  CUtensorMap mq, mkh, mvh;
+  if ((rc = make_map(&mq, q, p.bh, p.seqlen, 128, fa::kBlockM)) != FA_OK) return rc;
+  if ((rc = make_map(&mkh, k, p.bh, p.seqlen, 128, 64)) != FA_OK) return rc;          // half a K tile: 64 keys
+  if ((rc = make_map(&mvh, v, p.bh, p.seqlen, 128, fa::kBlockN, 1)) != FA_OK) return rc;  // half a V tile: one 64-wide panel
+  int clusters = s->num_sms / 2;
+  if (p.num_items < clusters) clusters = p.num_items;
+  if (alibi) fa::fwd_pair_kernel<true><<<2 * clusters, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mkh, mvh, p);
+  else fa::fwd_pair_kernel<false><<<2 * clusters, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mkh, mvh, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail_cuda("launch fwd_pair_kernel", e);
   return FA_OK;
 }
 
@@ -309,7 +334,8 @@ static int forward_impl(const void* q, const void* k, const void* v, void* o, in
        reinterpret_cast<uintptr_t>(o)) & 15)
     return fail(FA_INVALID_ARG, "tensor pointers must be 16-byte aligned");
   if ((long long)batch * heads > 0x7fffffffLL) return fail(FA_INVALID_ARG, "batch*heads overflows int");
-  if (kernel < 0 || kernel > 1) return fail(FA_INVALID_ARG, "kernel must be 0 (persistent) or 1 (serial)");
+  if (kernel < 0 || kernel > 2) return fail(FA_INVALID_ARG, "kernel must be 0 (default), 1 (serial) or 2 (CTA pair)");
+  if (kernel == 2 && head_dim != 128) return fail(FA_UNSUPPORTED, "the CTA-pair kernel needs head_dim 128");
   if (!(softmax_scale == softmax_scale)) return fail(FA_INVALID_ARG, "softmax_scale is NaN");
 
   DeviceState* s = nullptr;
@@ -358,6 +384,7 @@ static int forward_impl(const void* q, const void* k, const void* v, void* o, in
   if ((rc = make_map(&mv, v, bh, seqlen, head_dim, fa::kBlockN)) != FA_OK) return rc;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (kernel == 2) return launch_pair(s, q, k, v, p, st);
   if (kernel == 1) {
     return head_dim == 64 ? launch_serial<64>(s, mq, mk, mv, p, st) : launch_serial<128>(s, mq, mk, mv, p, st);
   }
