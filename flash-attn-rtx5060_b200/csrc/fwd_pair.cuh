@@ -211,6 +211,13 @@ fwd_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         if (!mbar_wait_warp(&s_full[s], n_s & 1, abort_flag)) { ok = false; break; }
         ++n_s;
         tc_fence_after();
+#ifdef FA_PAIR_FAKE  // bring-up only: the load + tensor pipeline of the pair without the softmax work
+        sAlpha[s * kBlockM + row_l] = 1.f;
+        __syncwarp();
+        if (lane == 0) { mbar_arrive(&alpha_ready[s]); mbar_arrive_cluster(p_full_even[s]); mbar_arrive_cluster(p_full2_even[s]); }
+        l_run = 1.f;
+        continue;
+#endif
         uint32_t r0[32], r1[32], r2[32], r3[32];
         tmem_ld32(tS + 0, r0);
         tmem_ld32(tS + 32, r1);
@@ -278,7 +285,9 @@ fwd_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
+#ifndef FA_PAIR_NOSPLIT
         if (lane == 0) mbar_arrive_cluster(p_full_even[s]);
+#endif
         if (masked) exp_half_tile<false>(sc + 64, scale2, negms2, pk1, lsum_a, lsum_b);
         else exp_half_tile<true>(sc + 64, scale2, negms2, pk1, lsum_a, lsum_b);
         tmem_st32(tS + 32, pk1);
@@ -288,7 +297,11 @@ fwd_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
+#ifndef FA_PAIR_NOSPLIT
         if (lane == 0) mbar_arrive_cluster(p_full2_even[s]);
+#else
+        if (lane == 0) mbar_arrive_cluster(p_full_even[s]);
+#endif
       }
       if (!ok) break;
       sRowSum[s * kBlockM + row_l] = l_run;
@@ -420,9 +433,11 @@ fwd_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                   umma_ts_2cta(tmem_base + colO, tmem_base + colS + kk * 8, vdesc + kk * (2048 >> 4), idesc_pv, 1u);
               }
               __syncwarp();
+#ifndef FA_PAIR_NOSPLIT
               if (!mbar_wait_cluster_warp(&p_full2[s], n_p[s] & 1, abort_flag)) { ok = false; break; }
-              ++n_p[s];
               tc_fence_after();
+#endif
+              ++n_p[s];
               if (elect_one()) {
 #pragma unroll
                 for (int kk = 4; kk < 8; ++kk)
