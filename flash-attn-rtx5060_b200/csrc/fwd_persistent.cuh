@@ -20,6 +20,8 @@
 // tiles, kv tiles outside a q tile's visible range are never loaded for it, and the output
 // is rescaled lazily.
 #pragma once
+#include <type_traits>
+
 #include "fwd_params.h"
 #include "ptx.cuh"
 
@@ -47,6 +49,20 @@
 #define FA_TR(cond, role, iter, slot) \
   do {                                \
   } while (0)
+#endif
+
+// Stamps of the tensor issuer: timeline entries under FA_TRACE; under FA_PROF (bring-up) each stamp
+// adds the clocks since the previous one to an accumulator chosen by the call site, and CTA 0
+// writes the sums to the dbg buffer.
+#if defined(FA_PROF)
+#define FA_TM(role, iter, slot)                                        \
+  do {                                                                 \
+    const uint32_t t_now = static_cast<uint32_t>(clock());             \
+    prof_acc[((role) == 5 ? 8 : 0) + (slot)] += t_now - prof_last;     \
+    prof_last = t_now;                                                 \
+  } while (0)
+#else
+#define FA_TM(role, iter, slot) FA_TR(lane == 0, role, iter, slot)
 #endif
 
 namespace fa {
@@ -473,68 +489,87 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       const uint32_t q_addr = smem_u32(sQ);
       const uint32_t kv_addr = smem_u32(sKV);
       const uint64_t qdesc[2] = {kdesc0 + (q_addr >> 4), kdesc0 + ((q_addr + Cfg::kTileBytes) >> 4)};
-      uint32_t it_base = 0;  // ring position of K tile lo_all of the current item
+      uint32_t ring_slot = 0, ring_par = 0;  // ring position (slot, phase parity) of K tile lo_all of the current item
       uint32_t n_p[2] = {0, 0}, n_q[2] = {0, 0};
       uint32_t n_items = 0;
       bool ok = true;
+#ifdef FA_PROF
+      uint32_t prof_acc[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+      uint32_t prof_last = static_cast<uint32_t>(clock());
+#endif
       while (ok) {
         const int item = take_item(n_items);
         if (item < 0) break;
         const ItemGeom g = decode_item(item, p);
-        for (int j = g.lo_all - 1; j < g.hi_all && ok; ++j) {
+        // Ring positions are carried along instead of recomputed: (slot_v, par_v) is where V_j lives,
+        // (slot_k, par_k) where K_{j+1} lives. Rounds in which both stages have a P.V for tile j and a
+        // score tile j+1 ("interior", nearly all of a long sequence) take a branch-free body; the first
+        // and last rounds of an item take the general one.
+        uint32_t slot_k = ring_slot, par_k = ring_par;  // K_{lo_all}
+        uint32_t slot_v = 0, par_v = 0;                 // set when j reaches lo_all
+        auto advance = [](uint32_t& slot, uint32_t& par, uint32_t n) {
+          slot += n;
+          if (slot >= static_cast<uint32_t>(Cfg::kStages)) { slot -= Cfg::kStages; par ^= 1u; }
+        };
+        // interior rounds in_lo <= j < in_hi: for both stages tile j is neither the first (its P.V accumulates)
+        // nor among the last two (no Q release, no final commit), and tile j+1 exists
+        const int in_lo = max(g.lo[0], g.lo[1]) + 1;
+        const int in_hi = min(g.hi[0], g.hi[1]) - 2;
+        auto round_body = [&](auto interior_tag, int j) {
+          constexpr bool kInterior = decltype(interior_tag)::value;
 #pragma unroll
           for (int s = 0; s < 2; ++s) {
-            const bool act_j = (j >= g.lo[s] && j < g.hi[s]);
-            const bool act_n = (j + 1 >= g.lo[s] && j + 1 < g.hi[s]);
-            const bool other_j = (s == 0) && (j >= g.lo[1] && j < g.hi[1]);          // stage 1 still needs V_j
-            const bool other_n = (s == 0) && (j + 1 >= g.lo[1] && j + 1 < g.hi[1]);  // stage 1 still needs K_j+1
+            const bool act_j = kInterior || (j >= g.lo[s] && j < g.hi[s]);
+            const bool act_n = kInterior || (j + 1 >= g.lo[s] && j + 1 < g.hi[s]);
+            const bool other_j = (s == 0) && (kInterior || (j >= g.lo[1] && j < g.hi[1]));          // stage 1 still needs V_j
+            const bool other_n = (s == 0) && (kInterior || (j + 1 >= g.lo[1] && j + 1 < g.hi[1]));  // stage 1 still needs K_j+1
             // stage 0 already waited for this tile in the same round
-            const bool v_seen = (s == 1) && (j >= g.lo[0] && j < g.hi[0]);
-            const bool k_seen = (s == 1) && (j + 1 >= g.lo[0] && j + 1 < g.hi[0]);
+            const bool v_seen = (s == 1) && (kInterior || (j >= g.lo[0] && j < g.hi[0]));
+            const bool k_seen = (s == 1) && (kInterior || (j + 1 >= g.lo[0] && j + 1 < g.hi[0]));
             const uint32_t colS = (s == 0) ? Cfg::kColS0 : Cfg::kColS1;
             const uint32_t colO = (s == 0) ? Cfg::kColO0 : Cfg::kColO1;
             if (act_j) {  // O_s += P_s(j) V_j, in two halves of 64 keys as P arrives
-              const uint32_t it = it_base + 2u * (j - g.lo_all) + 1u;
-              const uint32_t slot = it % Cfg::kStages;
-              const uint64_t vdesc = vdesc0 + ((kv_addr + slot * Cfg::kTileBytes) >> 4);
-              FA_TR(lane == 0, 3, j - g.lo_all + 1, s * 4 + 0);
-              if (!v_seen && !mbar_wait_warp(&kv_full[slot], (it / Cfg::kStages) & 1, abort_flag)) { ok = false; break; }
-              if (!mbar_wait_warp(&p_full[s], n_p[s] & 1, abort_flag)) { ok = false; break; }
+              const uint64_t vdesc = vdesc0 + ((kv_addr + slot_v * Cfg::kTileBytes) >> 4);
+              FA_TM(3, j - g.lo_all + 1, s * 4 + 0);
+              if (!v_seen && !mbar_wait_warp(&kv_full[slot_v], par_v, abort_flag)) { ok = false; return; }
+#ifndef FA_FAKE_NOWAIT  // (bring-up only: lets the issuer run without the softmax hand-shake)
+              if (!mbar_wait_warp(&p_full[s], n_p[s] & 1, abort_flag)) { ok = false; return; }
+#endif
               tc_fence_after();
-              FA_TR(lane == 0, 3, j - g.lo_all + 1, s * 4 + 1);
+              FA_TM(3, j - g.lo_all + 1, s * 4 + 1);
               if (elect_one()) {
-                umma_ts(tmem_base + colO, tmem_base + colS, vdesc, idesc_pv, (j > g.lo[s]) ? 1u : 0u);
+                umma_ts(tmem_base + colO, tmem_base + colS, vdesc, idesc_pv, (kInterior || j > g.lo[s]) ? 1u : 0u);
 #pragma unroll
                 for (int kk = 1; kk < 4; ++kk)
                   umma_ts(tmem_base + colO, tmem_base + colS + kk * 8, vdesc + kk * (2048 >> 4), idesc_pv, 1u);
               }
               __syncwarp();
-              FA_TR(lane == 0, 3, j - g.lo_all + 1, s * 4 + 2);
-              if (!mbar_wait_warp(&p_full2[s], n_p[s] & 1, abort_flag)) { ok = false; break; }
+              FA_TM(3, j - g.lo_all + 1, s * 4 + 2);
+#ifndef FA_FAKE_NOWAIT
+              if (!mbar_wait_warp(&p_full2[s], n_p[s] & 1, abort_flag)) { ok = false; return; }
+#endif
               ++n_p[s];
               tc_fence_after();
-              FA_TR(lane == 0, 3, j - g.lo_all + 1, s * 4 + 3);
+              FA_TM(3, j - g.lo_all + 1, s * 4 + 3);
               if (elect_one()) {
 #pragma unroll
                 for (int kk = 4; kk < 8; ++kk)
                   umma_ts(tmem_base + colO, tmem_base + colS + kk * 8, vdesc + kk * (2048 >> 4), idesc_pv, 1u);
-                if (!other_j) umma_commit(&kv_empty[slot]);
-                if (j + 1 == g.hi[s]) umma_commit(&o_full[s]);
+                if (!other_j) umma_commit(&kv_empty[slot_v]);
+                if (!kInterior && j + 1 == g.hi[s]) umma_commit(&o_full[s]);
               }
               __syncwarp();
-              FA_TR(lane == 0, 5, j - g.lo_all + 1, s * 4 + 0);
+              FA_TM(5, j - g.lo_all + 1, s * 4 + 0);
             }
             if (act_n) {  // S_s = Q_s K_{j+1}^T
-              const uint32_t it = it_base + 2u * (j + 1 - g.lo_all);
-              const uint32_t slot = it % Cfg::kStages;
-              if (j + 1 == g.lo[s]) {
-                if (!mbar_wait_warp(&q_full[s], n_q[s] & 1, abort_flag)) { ok = false; break; }
+              if (!kInterior && j + 1 == g.lo[s]) {
+                if (!mbar_wait_warp(&q_full[s], n_q[s] & 1, abort_flag)) { ok = false; return; }
                 ++n_q[s];
               }
-              if (!k_seen && !mbar_wait_warp(&kv_full[slot], (it / Cfg::kStages) & 1, abort_flag)) { ok = false; break; }
+              if (!k_seen && !mbar_wait_warp(&kv_full[slot_k], par_k, abort_flag)) { ok = false; return; }
               tc_fence_after();
-              FA_TR(lane == 0, 5, j - g.lo_all + 1, s * 4 + 1);
-              const uint64_t kdesc = kdesc0 + ((kv_addr + slot * Cfg::kTileBytes) >> 4);
+              FA_TM(5, j - g.lo_all + 1, s * 4 + 1);
+              const uint64_t kdesc = kdesc0 + ((kv_addr + slot_k * Cfg::kTileBytes) >> 4);
               if (elect_one()) {
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k) {
@@ -542,16 +577,35 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                   umma_ss(tmem_base + colS, qdesc[s] + off, kdesc + off, idesc_qk, k > 0 ? 1u : 0u);
                 }
                 umma_commit(&s_full[s]);
-                if (!other_n) umma_commit(&kv_empty[slot]);
-                if (j + 2 == g.hi[s]) umma_commit(&q_empty[s]);
+                if (!other_n) umma_commit(&kv_empty[slot_k]);
+                if (!kInterior && j + 2 == g.hi[s]) umma_commit(&q_empty[s]);
               }
               __syncwarp();
-              FA_TR(lane == 0, 5, j - g.lo_all + 1, s * 4 + 2);
+              FA_TM(5, j - g.lo_all + 1, s * 4 + 2);
             }
           }
+        };
+        for (int j = g.lo_all - 1; j < g.hi_all && ok; ++j) {
+          if (j >= in_lo && j < in_hi) round_body(std::true_type{}, j);
+          else round_body(std::false_type{}, j);
+          // V_{j+1} sits right after K_{j+1}; K_{j+2} two positions after K_{j+1}
+          slot_v = slot_k;
+          par_v = par_k;
+          advance(slot_v, par_v, 1);
+          advance(slot_k, par_k, 2);
         }
-        it_base += 2u * (g.hi_all - g.lo_all);
+        {  // the next item's K_{lo_all} follows this item's last V
+          uint32_t n = 2u * static_cast<uint32_t>(g.hi_all - g.lo_all);
+          while (n >= static_cast<uint32_t>(Cfg::kStages)) { n -= Cfg::kStages; ring_par ^= 1u; }
+          advance(ring_slot, ring_par, n);
+        }
       }
+#ifdef FA_PROF
+      if (blockIdx.x == 0 && p.dbg != nullptr && lane == 0) {
+        long long* out = reinterpret_cast<long long*>(p.dbg) + 3 * 16;
+        for (int i = 0; i < 16; ++i) out[i] = prof_acc[i];
+      }
+#endif
     } else if (warp == 13 && lane == 0) {
       // ===================================================================================
       // TMA producer
@@ -589,8 +643,15 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             const uint32_t slot = it % Cfg::kStages;
             if (!mbar_wait(&kv_empty[slot], ((it / Cfg::kStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
             FA_TR(true, 4, j - g.lo_all, t * 2 + 0);
-            mbar_arrive_expect_tx(&kv_full[slot], Cfg::kTileBytes);
-            tma_load_4d(sKV + slot * Cfg::kTileBytes, t == 0 ? &mapK : &mapV, &kv_full[slot], 0, j * kBlockN, 0, g.bh);
+#ifdef FA_FAKE_LOADS  // bring-up only: after the ring has been filled once, tiles "arrive" without being loaded
+            if (it >= Cfg::kStages) {
+              mbar_arrive(&kv_full[slot]);
+            } else
+#endif
+            {
+              mbar_arrive_expect_tx(&kv_full[slot], Cfg::kTileBytes);
+              tma_load_4d(sKV + slot * Cfg::kTileBytes, t == 0 ? &mapK : &mapV, &kv_full[slot], 0, j * kBlockN, 0, g.bh);
+            }
             ++it;
           }
         }
