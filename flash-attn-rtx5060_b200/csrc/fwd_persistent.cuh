@@ -308,88 +308,92 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         l_run = 1.f;
         continue;
 #endif
-        uint32_t r0[32], r1[32], r2[32], r3[32];
-        tmem_ld32(tS + 0, r0);
-        tmem_ld32(tS + 32, r1);
-        tmem_ld32(tS + 64, r2);
-        tmem_ld32(tS + 96, r3);
-        tmem_wait_ld();
-        tmem_ld_fence(r0);
-        tmem_ld_fence(r1);
-        tmem_ld_fence(r2);
-        tmem_ld_fence(r3);
-        FA_TR(row_l == 0, s, j - j_lo, 1);
-        float sc[kBlockN];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          sc[i] = __uint_as_float(r0[i]);
-          sc[32 + i] = __uint_as_float(r1[i]);
-          sc[64 + i] = __uint_as_float(r2[i]);
-          sc[96 + i] = __uint_as_float(r3[i]);
-        }
         const int kv0 = j * kBlockN;
-        if (kAlibi) {  // s * scale - slope * |i - j|, in log2 units (reference: src/mask.h:21-26, src/main.cu:200-207)
-          const float rel = static_cast<float>(row - kv0);
-#pragma unroll
-          for (int c = 0; c < kBlockN; ++c)
-            sc[c] = fmaf(sc[c], p.scale_log2, -slope_l2 * fabsf(rel - static_cast<float>(c)));
-        }
-        const bool masked = kv_tile_needs_mask(kv0, q_r0, q_r1, wl, wr, N);
-        if (masked) {
-          const int c_lo = (wl >= 0) ? row - wl - kv0 : -1;
-          int c_hi = N - 1 - kv0;
-          if (wr >= 0) c_hi = min(c_hi, row + wr - kv0);
-#pragma unroll
-          for (int c = 0; c < kBlockN; ++c)
-            if (c < c_lo || c > c_hi) sc[c] = -INFINITY;
-        }
-        float mx0 = m_run, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-        for (int c = 0; c < kBlockN; c += 8) {
-          mx0 = max3(mx0, sc[c], sc[c + 1]);
-          mx1 = max3(mx1, sc[c + 2], sc[c + 3]);
-          mx2 = max3(mx2, sc[c + 4], sc[c + 5]);
-          mx3 = max3(mx3, sc[c + 6], sc[c + 7]);
-        }
-        const float m_new = max3(mx0, mx1, fmaxf(mx2, mx3));
-        // Lazy rescale: keep the old reference max unless the true max moved by more than
-        // kLazyLog2 (P then stays below 2^8, well inside fp16), or no finite score was seen yet.
-        float alpha = 1.f;
-        if (m_run == -INFINITY) {
-          m_used = (m_new == -INFINITY) ? 0.f : m_new;
-        } else if ((m_new - m_used) * sl2 > Cfg::kLazyLog2) {
-          alpha = ex2_approx((m_used - m_new) * sl2);
-          m_used = m_new;
-        }
-        m_run = m_new;
-        sAlpha[s * kBlockM + row_l] = alpha;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&alpha_ready[s]);
-        FA_TR(row_l == 0, s, j - j_lo, 2);
+        // One body, instantiated twice: tiles cut by a mask boundary (or by the end of the sequence) take
+        // the per-element predicate and MUFU-only exponentials, all others carry none of that code.
+        auto tile_body = [&](auto masked_tag) {
+          constexpr bool kMasked = decltype(masked_tag)::value;
+          uint32_t r0[32], r1[32], r2[32], r3[32];
+          tmem_ld32(tS + 0, r0);
+          tmem_ld32(tS + 32, r1);
+          tmem_ld32(tS + 64, r2);
+          tmem_ld32(tS + 96, r3);
+          tmem_wait_ld();
+          tmem_ld_fence(r0);
+          tmem_ld_fence(r1);
+          tmem_ld_fence(r2);
+          tmem_ld_fence(r3);
+          FA_TR(row_l == 0, s, j - j_lo, 1);
+          float sc[kBlockN];
+  #pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            sc[i] = __uint_as_float(r0[i]);
+            sc[32 + i] = __uint_as_float(r1[i]);
+            sc[64 + i] = __uint_as_float(r2[i]);
+            sc[96 + i] = __uint_as_float(r3[i]);
+          }
+          if (kAlibi) {  // s * scale - slope * |i - j|, in log2 units (reference: src/mask.h:21-26, src/main.cu:200-207)
+            const float rel = static_cast<float>(row - kv0);
+  #pragma unroll
+            for (int c = 0; c < kBlockN; ++c)
+              sc[c] = fmaf(sc[c], p.scale_log2, -slope_l2 * fabsf(rel - static_cast<float>(c)));
+          }
+          if (kMasked) {
+            const int c_lo = (wl >= 0) ? row - wl - kv0 : -1;
+            int c_hi = N - 1 - kv0;
+            if (wr >= 0) c_hi = min(c_hi, row + wr - kv0);
+  #pragma unroll
+            for (int c = 0; c < kBlockN; ++c)
+              if (c < c_lo || c > c_hi) sc[c] = -INFINITY;
+          }
+          float mx0 = m_run, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+  #pragma unroll
+          for (int c = 0; c < kBlockN; c += 8) {
+            mx0 = max3(mx0, sc[c], sc[c + 1]);
+            mx1 = max3(mx1, sc[c + 2], sc[c + 3]);
+            mx2 = max3(mx2, sc[c + 4], sc[c + 5]);
+            mx3 = max3(mx3, sc[c + 6], sc[c + 7]);
+          }
+          const float m_new = max3(mx0, mx1, fmaxf(mx2, mx3));
+          // Lazy rescale, branch-free: the reference max moves only when the true max has grown by more
+          // than kLazyLog2 (P then stays below 2^8, well inside fp16) or when no finite score was seen
+          // before; otherwise alpha = 2^0 = 1 exactly.
+          const bool fresh = (m_run == -INFINITY);
+          const bool move = fresh || (m_new - m_used) * sl2 > Cfg::kLazyLog2;
+          const float m_next = move ? ((m_new == -INFINITY) ? 0.f : m_new) : m_used;
+          float alpha = ex2_approx((m_used - m_next) * sl2);
+          alpha = fresh ? 1.f : alpha;
+          m_used = m_next;
+          m_run = m_new;
+          sAlpha[s * kBlockM + row_l] = alpha;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&alpha_ready[s]);
+          FA_TR(row_l == 0, s, j - j_lo, 2);
 
-        const float neg_ms = -m_used * sl2;
-        const uint64_t negms2 = f2_pack(neg_ms, neg_ms);
-        uint64_t lsum_a = 0ull, lsum_b = 0ull;
-        uint32_t pk0[32], pk1[32];
-        // masked tiles hold -inf scores, which only the MUFU path maps to 0
-        if (masked) exp_half_tile<false>(sc, scale2, negms2, pk0, lsum_a, lsum_b);
-        else exp_half_tile<true>(sc, scale2, negms2, pk0, lsum_a, lsum_b);
-        tmem_st32(tS + 0, pk0);
-        tmem_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&p_full[s]);  // P of keys 0..63 is in TMEM
-        FA_TR(row_l == 0, s, j - j_lo, 3);
-        if (masked) exp_half_tile<false>(sc + 64, scale2, negms2, pk1, lsum_a, lsum_b);
-        else exp_half_tile<true>(sc + 64, scale2, negms2, pk1, lsum_a, lsum_b);
-        tmem_st32(tS + 32, pk1);
-        float l0, l1;
-        f2_unpack(f2_add(lsum_a, lsum_b), l0, l1);
-        l_run = l_run * alpha + (l0 + l1);
-        tmem_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&p_full2[s]);  // P of keys 64..127
+          const float neg_ms = -m_used * sl2;
+          const uint64_t negms2 = f2_pack(neg_ms, neg_ms);
+          uint64_t lsum_a = 0ull, lsum_b = 0ull;
+          uint32_t pk0[32], pk1[32];
+          // masked tiles hold -inf scores, which only the MUFU path maps to 0
+          exp_half_tile<!kMasked>(sc, scale2, negms2, pk0, lsum_a, lsum_b);
+          tmem_st32(tS + 0, pk0);
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&p_full[s]);  // P of keys 0..63 is in TMEM
+          FA_TR(row_l == 0, s, j - j_lo, 3);
+          exp_half_tile<!kMasked>(sc + 64, scale2, negms2, pk1, lsum_a, lsum_b);
+          tmem_st32(tS + 32, pk1);
+          float l0, l1;
+          f2_unpack(f2_add(lsum_a, lsum_b), l0, l1);
+          l_run = l_run * alpha + (l0 + l1);
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&p_full2[s]);  // P of keys 64..127
+        };
+        if (kv_tile_needs_mask(kv0, q_r0, q_r1, wl, wr, N)) tile_body(std::true_type{});
+        else tile_body(std::false_type{});
         FA_TR(row_l == 0, s, j - j_lo, 4);
       }
       if (!ok) break;
