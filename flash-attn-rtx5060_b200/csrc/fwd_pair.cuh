@@ -124,7 +124,7 @@ fwd_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   uint64_t* alpha_ready = bars + 8;   // [2] own softmax -> own correction
   uint64_t* l_ready = bars + 10;      // [2] own softmax -> own correction
   uint64_t* o_full = bars + 12;       // [2] MMA (multicast) -> own correction
-  uint64_t* p_full2 = bars + 14;      // [2] even CTA only: softmax warps of both CTAs -> MMA
+  uint64_t* p_full2 = bars + 14;      // [2] unused (P is handed over whole: every hand-off crosses the pair)
   uint64_t* q_peer = bars + 16;       // [2] even CTA only: the odd CTA's Q tile has landed
   uint64_t* kv_full = bars + 18;                       // [kStages] own TMA -> MMA / relay
   uint64_t* kv_empty = bars + 18 + Cfg::kStages;       // [kStages] MMA (multicast) -> own TMA
@@ -143,7 +143,7 @@ fwd_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       mbar_init(&q_empty[s], 1);
       mbar_init(&s_full[s], 1);
       mbar_init(&p_full[s], 16);  // 4 softmax + 4 correction warps of each CTA
-      mbar_init(&p_full2[s], 8);  // 4 softmax warps of each CTA
+      mbar_init(&p_full2[s], 8);
       mbar_init(&alpha_ready[s], 4);
       mbar_init(&l_ready[s], 4);
       mbar_init(&o_full[s], 1);
@@ -173,7 +173,6 @@ fwd_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   const int wr = eff_window_right(p.causal, p.window_right);
   // barriers of the even CTA that both CTAs arrive on
   const uint32_t p_full_even[2] = {mapa_u32(smem_u32(&p_full[0]), 0), mapa_u32(smem_u32(&p_full[1]), 0)};
-  const uint32_t p_full2_even[2] = {mapa_u32(smem_u32(&p_full2[0]), 0), mapa_u32(smem_u32(&p_full2[1]), 0)};
 
   if (misaligned) {
     // swizzled tiles need a 1024-byte aligned base; nothing was issued, fall through to the common exit
@@ -181,7 +180,7 @@ fwd_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     // =====================================================================================
     // softmax: stage s = warp / 4, row = tid % 128 of this CTA's tile of that stage
     // =====================================================================================
-    reg_inc<FA_REG_SOFTMAX>();
+    reg_inc<168>();
     const int s = warp >> 2;
     const int row_l = tid & 127;
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32u;
@@ -214,7 +213,7 @@ fwd_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 #ifdef FA_PAIR_FAKE  // bring-up only: the load + tensor pipeline of the pair without the softmax work
         sAlpha[s * kBlockM + row_l] = 1.f;
         __syncwarp();
-        if (lane == 0) { mbar_arrive(&alpha_ready[s]); mbar_arrive_cluster(p_full_even[s]); mbar_arrive_cluster(p_full2_even[s]); }
+        if (lane == 0) { mbar_arrive(&alpha_ready[s]); mbar_arrive_cluster(p_full_even[s]); }
         l_run = 1.f;
         continue;
 #endif
@@ -285,9 +284,6 @@ fwd_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-#ifndef FA_PAIR_NOSPLIT
-        if (lane == 0) mbar_arrive_cluster(p_full_even[s]);
-#endif
         if (masked) exp_half_tile<false>(sc + 64, scale2, negms2, pk1, lsum_a, lsum_b);
         else exp_half_tile<true>(sc + 64, scale2, negms2, pk1, lsum_a, lsum_b);
         tmem_st32(tS + 32, pk1);
@@ -297,11 +293,7 @@ fwd_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-#ifndef FA_PAIR_NOSPLIT
-        if (lane == 0) mbar_arrive_cluster(p_full2_even[s]);
-#else
-        if (lane == 0) mbar_arrive_cluster(p_full_even[s]);
-#endif
+        if (lane == 0) mbar_arrive_cluster(p_full_even[s]);  // the whole P tile is in TMEM
       }
       if (!ok) break;
       sRowSum[s * kBlockM + row_l] = l_run;
@@ -312,7 +304,7 @@ fwd_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     // =====================================================================================
     // correction + epilogue for this CTA's rows of both stages
     // =====================================================================================
-    reg_dec<FA_REG_CORR>();
+    reg_dec<96>();
     const int row_l = tid & 127;
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32u;
     uint32_t n_alpha[2] = {0, 0}, n_l[2] = {0, 0}, n_o[2] = {0, 0};
@@ -384,7 +376,7 @@ fwd_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       }
     }
   } else {
-    reg_dec<FA_REG_MISC>();
+    reg_dec<80>();
     if (warp == 12 && rank == 0) {
       // ===================================================================================
       // tensor-core issuer of the pair (even CTA)
@@ -415,7 +407,7 @@ fwd_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             const bool k_seen = (s == 1) && g.on[0] && (j + 1 >= g.lo[0] && j + 1 < g.hi[0]);
             const uint32_t colS = (s == 0) ? Cfg::kColS0 : Cfg::kColS1;
             const uint32_t colO = (s == 0) ? Cfg::kColO0 : Cfg::kColO1;
-            if (act_j) {  // O_s += P_s(j) V_j for both CTAs, in two halves of 64 keys
+            if (act_j) {  // O_s += P_s(j) V_j for both CTAs
               const uint32_t it = it_base + 2u * (j - g.lo_all) + 1u;
               const uint32_t slot = it % Cfg::kStages;
               const uint32_t par = (it / Cfg::kStages) & 1u;
@@ -433,10 +425,6 @@ fwd_pair_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                   umma_ts_2cta(tmem_base + colO, tmem_base + colS + kk * 8, vdesc + kk * (2048 >> 4), idesc_pv, 1u);
               }
               __syncwarp();
-#ifndef FA_PAIR_NOSPLIT
-              if (!mbar_wait_cluster_warp(&p_full2[s], n_p[s] & 1, abort_flag)) { ok = false; break; }
-              tc_fence_after();
-#endif
               ++n_p[s];
               if (elect_one()) {
 #pragma unroll

@@ -56,7 +56,8 @@ int flash_forward_alibi(const void* q, const void* k, const void* v, void* o, in
                         const float* alibi_slopes, void* stream);
 
 /* Same operation with an explicit kernel choice, for tests and bring-up:
- *   kernel  0 = default (warp-specialised persistent kernel), 1 = serial one-tile-per-CTA kernel
+ *   kernel  0 = default (warp-specialised persistent kernel), 1 = serial one-tile-per-CTA kernel,
+ *           2 = CTA-pair kernel (cta_group::2 MMA over a cluster of two CTAs, head_dim 128 only)
  *   variant kernel-specific switches (serial kernel: bit0 stages P in shared memory)
  *   dbg     optional device buffer of 128*128 + 128*head_dim floats receiving the raw first
  *           score tile and first P.V product of q tile 0 / head 0 (serial kernel), else NULL

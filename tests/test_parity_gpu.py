@@ -154,6 +154,21 @@ def test_edge_shapes_and_windows(pkg, ob, kernel, N, d, causal, wl, wr):
     assert_close(ob, got, want)
 
 
+@pytest.mark.parametrize("N,causal,wl,wr", [
+    (512, False, -1, -1), (1024, True, -1, -1), (1000, True, -1, -1), (333, False, -1, -1), (1024, True, 256, -1),
+    (700, False, 100, 50), (2048, True, 1024, -1), (129, True, -1, -1),
+])
+def test_cta_pair_kernel(pkg, ob, N, causal, wl, wr):
+    """The cta_group::2 variant (two CTAs share every K/V tile; head_dim 128 only), flash_forward_ex(kernel=2)."""
+    q, k, v = make_inputs(N * 3 + 1, 2, 3, N, 128)
+    got = run_gpu(pkg, q, k, v, causal, wl, wr, kernel=2)
+    want = ob.attention(q, k, v, causal=causal, window_left=wl, window_right=wr)
+    assert_close(ob, got, want)
+    ref = run_gpu(pkg, q, k, v, causal, wl, wr, kernel=0)
+    mx, mean, nans = ob.abs_error(got, ref)
+    assert nans == 0 and mx <= 2e-3
+
+
 def exact_attention(q, k, v, scale, causal):
     """fp64 attention of fp16 inputs (numpy), rounded once to fp16: the error-free answer."""
     q64, k64, v64 = (a.astype(np.float64) for a in (q, k, v))
