@@ -39,6 +39,12 @@ OTHER_CONFIGS = [
     dict(name="C3", B=2, H=32, N=8192, d=128, causal=True, wl=-1, wr=-1),
     dict(name="C4", B=4, H=16, N=16384, d=128, causal=True, wl=1024, wr=-1),
 ]
+# 12 heads of the workload's own per-head shape (two head groups of 6): the case the DRAM-traffic capture runs on;
+# traffic per head carries over to the full workload because heads are scheduled in groups of 6 there too.
+TRAFFIC_CASE = dict(name="C5s", B=1, H=12, N=32768, d=128, causal=True, wl=-1, wr=-1)
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of TRAFFIC_CASE under ncu (677.5 MB + 86.9 MB for 12
+# heads; profiles/fwd_persistent_d128_causal_N32768_traffic.md), per head. Algorithmic bytes per head are 33.6 MB.
+TRAFFIC_BYTES_PER_HEAD = (677522944 + 86895104) / 12
 METRIC = "fwd attention TFLOP/s (whole job; FLOPs = 4*B*H*N^2*d, halved for causal)"
 FALLBACK_TFLOPS = 1590.0  # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
 
@@ -236,7 +242,7 @@ def main():
     stream = torch.cuda.Stream()
 
     if args.case:
-        c = next(x for x in OTHER_CONFIGS if x["name"] == args.case)
+        c = next(x for x in OTHER_CONFIGS + [TRAFFIC_CASE] if x["name"] == args.case)
         ms, fl_c, _ = time_config(pkg, torch, c, c["B"] * c["H"], args.steps, args.warmup, stream)
         print(json.dumps(dict(case=c["name"], ms=ms, tflops=fl_c / (ms * 1e-3) / 1e12, steps=args.steps,
                               note="profiling aid, not a benchmark line")))
@@ -350,7 +356,9 @@ def main():
     achieved = flops_rank / (kernel_ms * 1e-3) / 1e12
     # each timed step is one ~0.1 s launch inside a seconds-long loop under the power cap
     roofline = dict(bound="tensor", achieved=achieved, peak=pk["sustained"], unit="TFLOP/s", frac=achieved / pk["sustained"],
-                    traffic=None, peak_source=f"{pk['source']} bf16 GEMM, sustained figure (kernel timed inside a long loop)",
+                    traffic=TRAFFIC_BYTES_PER_HEAD * heads, traffic_unit="bytes per launch",
+                    traffic_source="ncu capture of 12 heads of the same per-head shape, scaled by heads per launch",
+                    algorithmic_bytes=4.0 * heads * N * d * 2, peak_source=f"{pk['source']} bf16 GEMM, sustained figure (kernel timed inside a long loop)",
                     frac_of_burst_peak=achieved / pk["burst"], burst_peak=pk["burst"],
                     kernel="fwd_persistent_kernel<128>", launch_ms=kernel_ms, flops_per_launch=flops_rank)
     per_config = []
