@@ -25,6 +25,8 @@ EXPORTS = (
     "flash_forward",
     "flash_forward_ex",
     "flash_forward_alibi",
+    "flash_forward_lse",
+    "flash_forward_multi_gpu",
     "flash_forward_host",
     "flash_forward_host_workspace_bytes",
     "flash_forward_check",
@@ -58,6 +60,11 @@ def lib():
     L.flash_forward.restype = i
     L.flash_forward_alibi.argtypes = [vp, vp, vp, vp, i, i, i, i, f, i, i, i, vp, vp]
     L.flash_forward_alibi.restype = i
+    L.flash_forward_lse.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, f, i, i, i, vp, vp]
+    L.flash_forward_lse.restype = i
+    pp = ctypes.POINTER(vp)
+    L.flash_forward_multi_gpu.argtypes = [i, ctypes.POINTER(i), pp, pp, pp, pp, ctypes.POINTER(i), i, i, f, i, i, i, pp, i]
+    L.flash_forward_multi_gpu.restype = i
     L.flash_forward_ex.argtypes = [vp, vp, vp, vp, i, i, i, i, f, i, i, i, vp, i, i, vp]
     L.flash_forward_ex.restype = i
     L.flash_forward_host.argtypes = [vp, vp, vp, vp, i, i, i, i, f, i, i, i, vp, ctypes.c_size_t, i]
@@ -92,6 +99,20 @@ def flash_forward(q, k, v, o, batch, heads, seqlen, head_dim, softmax_scale=0.0,
     """Enqueues the attention forward on raw device pointers (ints). Asynchronous."""
     rc = lib().flash_forward_ex(q, k, v, o, batch, heads, seqlen, head_dim, softmax_scale, int(bool(is_causal)),
                                 window_left, window_right, stream, kernel, variant, dbg)
+    if rc != FA_OK:
+        _raise(rc)
+
+
+def flash_forward_multi_gpu(devices, q, k, v, o, slab_heads, seqlen, head_dim, softmax_scale=0.0, is_causal=False,
+                            window_left=-1, window_right=-1, streams=None, wait=True):
+    """One slab of heads per entry of `devices`; q, k, v, o are lists of raw device pointers (ints)."""
+    n = len(devices)
+    assert len(q) == len(k) == len(v) == len(o) == len(slab_heads) == n
+    ints = lambda xs: (ctypes.c_int * n)(*xs)  # noqa: E731
+    ptrs = lambda xs: (ctypes.c_void_p * n)(*xs)  # noqa: E731
+    rc = lib().flash_forward_multi_gpu(n, ints(devices), ptrs(q), ptrs(k), ptrs(v), ptrs(o), ints(slab_heads), seqlen,
+                                       head_dim, softmax_scale, int(bool(is_causal)), window_left, window_right,
+                                       None if streams is None else ptrs(streams), int(bool(wait)))
     if rc != FA_OK:
         _raise(rc)
 
@@ -146,10 +167,11 @@ def run_flash_attention(B, N, S, d, Q, K, V, O, L=None, M=None, Is_dropout=False
 
 
 def attention_forward(q, k, v, causal=False, window_left=-1, window_right=-1, softmax_scale=0.0, out=None, kernel=0,
-                      variant=0, alibi_slopes=None):
+                      variant=0, alibi_slopes=None, return_lse=False):
     """Convenience wrapper for torch CUDA tensors of shape [B, H, N, d], fp16, contiguous.
 
     torch is used for device memory and the current stream only; the computation is the library's.
+    With return_lse the result is (out, lse), lse a float32 [B, H, N] tensor (flash_forward_lse).
     """
     import torch
 
@@ -160,6 +182,17 @@ def attention_forward(q, k, v, causal=False, window_left=-1, window_right=-1, so
         out = torch.empty_like(q)
     stream = torch.cuda.current_stream(q.device).cuda_stream
     with torch.cuda.device(q.device):
+        if alibi_slopes is not None:
+            assert alibi_slopes.is_cuda and alibi_slopes.dtype == torch.float32 and alibi_slopes.numel() == H
+        if return_lse:
+            assert kernel == 0 and variant == 0
+            lse = torch.empty((B, H, N), device=q.device, dtype=torch.float32)
+            rc = lib().flash_forward_lse(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), B, H,
+                                         N, d, softmax_scale, int(bool(causal)), window_left, window_right,
+                                         None if alibi_slopes is None else alibi_slopes.data_ptr(), stream)
+            if rc != FA_OK:
+                _raise(rc)
+            return out, lse
         if alibi_slopes is not None:  # float32 CUDA tensor with one slope per head
             assert alibi_slopes.is_cuda and alibi_slopes.dtype == torch.float32 and alibi_slopes.numel() == H
             rc = lib().flash_forward_alibi(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, H, N, d,

@@ -66,7 +66,7 @@ struct DeviceState {
   int num_sms = 0;
   int* status = nullptr;  // device words: [0] status, then kSchedSlots pairs of scheduler words
   unsigned next_sched = 0;
-  bool attr_set[8] = {};
+  bool attr_set[12] = {};
 };
 DeviceState g_dev[kMaxDevices];
 
@@ -165,13 +165,13 @@ int launch_pair(DeviceState* s, const void* q, const void* k, const void* v, fa:
   return FA_OK;
 }
 
-template <int D>
-int launch_persistent(DeviceState* s, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                      const fa::FwdParams& p, cudaStream_t st) {
+template <int D, bool kAlibi, bool kLse>
+int launch_persistent_as(DeviceState* s, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                         const fa::FwdParams& p, cudaStream_t st) {
   using Cfg = fa::PersistentCfg<D>;
-  const bool alibi = p.alibi_slopes != nullptr;
-  int rc = alibi ? ensure_smem_attr(s, D == 64 ? 4 : 5, fa::fwd_persistent_kernel<D, true>, Cfg::kSmemBytes)
-                 : ensure_smem_attr(s, D == 64 ? 2 : 3, fa::fwd_persistent_kernel<D, false>, Cfg::kSmemBytes);
+  // attribute slots 2..5 and 8..11: one per instantiation
+  constexpr int slot = (kLse ? 8 : 2) + (kAlibi ? 2 : 0) + (D == 64 ? 0 : 1);
+  int rc = ensure_smem_attr(s, slot, fa::fwd_persistent_kernel<D, kAlibi, kLse>, Cfg::kSmemBytes);
   if (rc != FA_OK) return rc;
   int grid = p.num_items < s->num_sms ? p.num_items : s->num_sms;
   fa::FwdParams pp = p;
@@ -179,11 +179,22 @@ int launch_persistent(DeviceState* s, const CUtensorMap& mq, const CUtensorMap& 
     std::lock_guard<std::mutex> lk(s->mu);
     pp.sched = s->status + 4 + 2 * (s->next_sched++ % kSchedSlots);
   }
-  if (alibi) fa::fwd_persistent_kernel<D, true><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mk, mv, pp);
-  else fa::fwd_persistent_kernel<D, false><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mk, mv, pp);
+  fa::fwd_persistent_kernel<D, kAlibi, kLse><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mk, mv, pp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail_cuda("launch fwd_persistent_kernel", e);
   return FA_OK;
+}
+
+// The ALiBi bias and the log-sum-exp output are compiled in only where asked for, so the plain
+// forward carries neither the per-element bias arithmetic nor the extra live values.
+template <int D>
+int launch_persistent(DeviceState* s, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                      const fa::FwdParams& p, cudaStream_t st) {
+  const bool alibi = p.alibi_slopes != nullptr, lse = p.lse != nullptr;
+  if (alibi) return lse ? launch_persistent_as<D, true, true>(s, mq, mk, mv, p, st)
+                        : launch_persistent_as<D, true, false>(s, mq, mk, mv, p, st);
+  return lse ? launch_persistent_as<D, false, true>(s, mq, mk, mv, p, st)
+             : launch_persistent_as<D, false, false>(s, mq, mk, mv, p, st);
 }
 
 // ---- host-buffer entry point -----------------------------------------------------------
@@ -325,8 +336,11 @@ int flash_forward_kv_range(int seqlen, int is_causal, int window_left, int windo
 
 static int forward_impl(const void* q, const void* k, const void* v, void* o, int batch, int heads, int seqlen,
                         int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,
-                        const float* alibi_slopes, void* stream, int kernel, int variant, float* dbg) {
+                        const float* alibi_slopes, void* stream, int kernel, int variant, float* dbg,
+                        float* lse = nullptr) {
   if (!q || !k || !v || !o) return fail(FA_INVALID_ARG, "null tensor pointer");
+  if (reinterpret_cast<uintptr_t>(lse) & 3) return fail(FA_INVALID_ARG, "lse must be 4-byte aligned");
+  if (lse && kernel != 0) return fail(FA_UNSUPPORTED, "only the default kernel writes the log-sum-exp");
   if (alibi_slopes && kernel == 1) return fail(FA_UNSUPPORTED, "the serial kernel has no ALiBi path");
   if (batch <= 0 || heads <= 0 || seqlen <= 0) return fail(FA_INVALID_ARG, "batch, heads and seqlen must be positive");
   if (head_dim != 64 && head_dim != 128) return fail(FA_UNSUPPORTED, "head_dim must be 64 or 128");
@@ -359,6 +373,7 @@ static int forward_impl(const void* q, const void* k, const void* v, void* o, in
   p.dbg = dbg;
   p.variant = variant;
   p.alibi_slopes = alibi_slopes;
+  p.lse = lse;
   p.heads = heads;
   p.num_q_pairs = (seqlen + 2 * fa::kBlockM - 1) / (2 * fa::kBlockM);
   if ((long long)bh * p.num_q_pairs > 0x7fffffffLL) return fail(FA_INVALID_ARG, "too many work items");
@@ -411,6 +426,41 @@ int flash_forward_alibi(const void* q, const void* k, const void* v, void* o, in
   if (!alibi_slopes) return fail(FA_INVALID_ARG, "alibi_slopes is null");
   return forward_impl(q, k, v, o, batch, heads, seqlen, head_dim, softmax_scale, is_causal, window_left, window_right,
                       alibi_slopes, stream, 0, 0, nullptr);
+}
+
+int flash_forward_lse(const void* q, const void* k, const void* v, void* o, float* lse, int batch, int heads,
+                      int seqlen, int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,
+                      const float* alibi_slopes, void* stream) {
+  if (!lse) return fail(FA_INVALID_ARG, "lse is null");
+  return forward_impl(q, k, v, o, batch, heads, seqlen, head_dim, softmax_scale, is_causal, window_left, window_right,
+                      alibi_slopes, stream, 0, 0, nullptr, lse);
+}
+
+int flash_forward_multi_gpu(int num_slabs, const int* devices, const void* const* q, const void* const* k,
+                            const void* const* v, void* const* o, const int* slab_heads, int seqlen, int head_dim,
+                            float softmax_scale, int is_causal, int window_left, int window_right,
+                            void* const* streams, int wait) {
+  if (num_slabs <= 0 || !devices || !q || !k || !v || !o || !slab_heads)
+    return fail(FA_INVALID_ARG, "num_slabs must be positive and the per-slab arrays non-null");
+  int prev = 0;
+  cudaError_t e = cudaGetDevice(&prev);
+  if (e != cudaSuccess) return fail_cuda("cudaGetDevice", e);
+  int rc = FA_OK;
+  // Enqueue on every device first (the launches are asynchronous, so the devices run side by side),
+  // then, if asked, wait for each and read its status word.
+  for (int i = 0; i < num_slabs && rc == FA_OK; ++i) {
+    if (slab_heads[i] == 0) continue;  // a device may be left without work
+    if ((e = cudaSetDevice(devices[i])) != cudaSuccess) { rc = fail_cuda("cudaSetDevice", e); break; }
+    rc = forward_impl(q[i], k[i], v[i], o[i], 1, slab_heads[i], seqlen, head_dim, softmax_scale, is_causal, window_left,
+                      window_right, nullptr, streams ? streams[i] : nullptr, 0, 0, nullptr);
+  }
+  for (int i = 0; wait && i < num_slabs && rc == FA_OK; ++i) {
+    if (slab_heads[i] == 0) continue;
+    if ((e = cudaSetDevice(devices[i])) != cudaSuccess) { rc = fail_cuda("cudaSetDevice", e); break; }
+    rc = flash_forward_check(streams ? streams[i] : nullptr);
+  }
+  cudaSetDevice(prev);
+  return rc;
 }
 
 int flash_forward_check(void* stream) {

@@ -31,6 +31,10 @@ struct FwdParams {
   const float* alibi_slopes;  // optional, one slope per head (device); the score of (i, j) gets
                               // -slope * |i - j| after scaling, as the reference does (src/mask.h:21-26)
   int heads;         // heads per batch entry (indexes alibi_slopes)
+  float* lse;        // optional [bh][seqlen] output: natural-log sum of exp(scaled, biased scores) over the
+                     // visible keys of each row (-inf for a row without visible keys); nullptr = not written
+                     // (persistent kernel only).
+                     // The reference declares L/M outputs (src/flash_forward.h:602-603) but never writes them.
   int* sched;        // device scratch, two words that are 0 between launches: [0] next work item to
                      // hand out (beyond the first gridDim.x), [1] CTAs that have finished
 };

@@ -172,7 +172,7 @@ __device__ __forceinline__ void exp_half_tile(const float* sc, uint64_t scale2, 
   }
 }
 
-template <int D, bool kAlibi>
+template <int D, bool kAlibi, bool kLse = false>
 __global__ void __launch_bounds__(512, 1)
 fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                       const __grid_constant__ CUtensorMap mapV, const FwdParams p) {
@@ -400,6 +400,11 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       sRowSum[s * kBlockM + row_l] = l_run;
       __syncwarp();
       if (lane == 0) mbar_arrive(&l_ready[s]);
+      // l_run = sum over visible keys of 2^((score - m_used) * sl2), so the natural-log sum of exponentials is
+      // ln2 * (m_used * sl2 + log2(l_run)).
+      if (kLse && row < N)
+        p.lse[static_cast<size_t>(g.bh) * N + row] =
+            (l_run > 0.f) ? 0.6931471805599453f * fmaf(m_used, sl2, __log2f(l_run)) : -INFINITY;
     }
   } else if (warp < 12) {
     // =====================================================================================

@@ -55,6 +55,33 @@ int flash_forward_alibi(const void* q, const void* k, const void* v, void* o, in
                         int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,
                         const float* alibi_slopes, void* stream);
 
+/* The forward that also returns the log-sum-exp of every query row:
+ *   lse[(b*heads + h)*seqlen + i] = ln( sum over visible keys j of exp(scale * q_i.k_j + bias_ij) )
+ * in fp32, device memory, batch*heads*seqlen floats. With O it is what a caller needs to merge
+ * attention over disjoint key ranges, or to start a backward pass. The reference's signature carries
+ * two outputs for this (`half* L`, `half* M`, src/flash_forward.h:602-603) and its parameter block has
+ * the fields (include/utils.h:149-150), but they are never assigned and its kernel never writes
+ * them; this entry point is the working form of that output, so its parity is pinned
+ * by the definition above (tests compare with an fp64 evaluation), not by reference vectors.
+ * alibi_slopes may be NULL (no bias). All other arguments as for flash_forward(). */
+int flash_forward_lse(const void* q, const void* k, const void* v, void* o, float* lse, int batch, int heads,
+                      int seqlen, int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,
+                      const float* alibi_slopes, void* stream);
+
+/* Several GPUs from one host thread. Every (batch, head) is an independent problem (the reference's CPU
+ * path loops over them, src/main.cu:179-186, and on its GPU a work item touches only its own head's
+ * rows, src/flash_forward.h:128,:134), so the heads are cut into slabs and each slab runs on its own
+ * device with no exchange between devices. Slab i: device ordinal devices[i], tensors q[i], k[i], v[i],
+ * o[i] resident on that device and laid out [slab_heads[i]][seqlen][head_dim], stream streams[i]
+ * (streams may be NULL: default streams). A slab with 0 heads is skipped; two slabs may name the same
+ * device. All launches are enqueued before anything is waited for; wait != 0 then synchronises each
+ * stream and reads each device's status word. The calling thread's current device is restored.
+ * The reference is single-GPU (device 0 hard-coded, src/flash_forward.h:374,:615). */
+int flash_forward_multi_gpu(int num_slabs, const int* devices, const void* const* q, const void* const* k,
+                            const void* const* v, void* const* o, const int* slab_heads, int seqlen, int head_dim,
+                            float softmax_scale, int is_causal, int window_left, int window_right,
+                            void* const* streams, int wait);
+
 /* Same operation with an explicit kernel choice, for tests and bring-up:
  *   kernel  0 = default (warp-specialised persistent kernel), 1 = serial one-tile-per-CTA kernel,
  *           2 = CTA-pair kernel (cta_group::2 MMA over a cluster of two CTAs, head_dim 128 only)

@@ -120,3 +120,34 @@ def abs_error(a, b):
     port().oracle_abs_error(a16.ctypes.data, b16.ctypes.data, a16.size, ctypes.byref(mx), ctypes.byref(mean),
                             ctypes.byref(nans))
     return mx.value, mean.value, nans.value
+
+
+def log_sum_exp_fp64(q, k, softmax_scale=0.0, causal=False, window_left=-1, window_right=-1, alibi_slopes=None,
+                     rows=None):
+    """Natural-log sum of exp(scale * q_i.k_j - slope_h * |i - j|) over the keys row i may see, in float64 (numpy).
+
+    The reference has no such output (its L/M arguments are dead, src/flash_forward.h:602-603), so this is
+    the mathematical definition evaluated exactly on the same fp16 inputs, with the reference's masks
+    (src/main.cu:200-222: ALiBi, causal j <= i, window |i - j| <= w, here two-sided with -1 = unbounded).
+    q, k: fp16 [B, H, N, d]; rows: optional 1-D index array. Returns float64 [B, H, len(rows) or N]."""
+    B, H, N, d = q.shape
+    scale = softmax_scale if softmax_scale > 0 else 1.0 / np.sqrt(d)
+    rows = np.arange(N) if rows is None else np.asarray(rows)
+    i = rows[:, None].astype(np.int64)
+    j = np.arange(N, dtype=np.int64)[None, :]
+    wr = 0 if causal else window_right
+    visible = np.ones((rows.size, N), dtype=bool)
+    if wr >= 0:
+        visible &= j <= i + wr
+    if window_left >= 0:
+        visible &= j >= i - window_left
+    out = np.empty((B, H, rows.size))
+    for b in range(B):
+        for h in range(H):
+            s = (q[b, h, rows].astype(np.float64) @ k[b, h].astype(np.float64).T) * scale
+            if alibi_slopes is not None:
+                s -= float(alibi_slopes[h]) * np.abs(i - j)
+            s = np.where(visible, s, -np.inf)
+            m = s.max(axis=1, keepdims=True)
+            out[b, h] = (m + np.log(np.exp(s - m).sum(axis=1, keepdims=True)))[:, 0]
+    return out

@@ -54,8 +54,14 @@ def test_argument_errors_are_status_codes(pkg):
     # ALiBi without slopes is a caller error
     assert L.run_flash_attention_c(1, 1, 128, 64, p, p, p, p, None, None, 0, 0, 0, 1, 0, None, 0.0, None) == pkg.FA_INVALID_ARG
     assert L.flash_forward_alibi(p, p, p, p, 1, 1, 128, 64, 0.0, 0, -1, -1, None, None) == pkg.FA_INVALID_ARG
+    # the log-sum-exp entry point needs its output buffer, 4-byte aligned
+    assert L.flash_forward_lse(p, p, p, p, None, 1, 1, 128, 64, 0.0, 0, -1, -1, None, None) == pkg.FA_INVALID_ARG
+    assert b"lse" in L.flash_forward_last_error()
+    assert L.flash_forward_lse(p, p, p, p, ctypes.c_void_p(0x1002), 1, 1, 128, 64, 0.0, 0, -1, -1, None, None) == pkg.FA_INVALID_ARG
     with pytest.raises(pkg.FlashForwardError):
         pkg.run_flash_attention(1, 1, 128, 64, 0x1000, 0x1000, 0x1000, 0x1000, Is_dropout=True)
+    with pytest.raises(pkg.FlashForwardError):  # no slabs
+        pkg.flash_forward_multi_gpu([], [], [], [], [], [], 128, 64)
 
 
 def test_no_gpu_is_an_error_not_a_fallback(pkg):

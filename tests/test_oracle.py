@@ -81,3 +81,30 @@ def test_abs_error_metric(ob):
     b = np.array([1.5, 2.0, 2.0, 0.0], dtype=np.float16)
     mx, mean, nans = ob.abs_error(a, b)
     assert mx == 1.0 and nans == 1 and abs(mean - 1.5 / 4) < 1e-12
+
+
+@pytest.mark.parametrize("causal,wl,wr,alibi", [(False, -1, -1, False), (True, -1, -1, False), (False, 40, 40, True)])
+def test_log_sum_exp_checker_agrees_with_the_oracle(ob, causal, wl, wr, alibi):
+    # The fp64 log-sum-exp the GPU's lse output is tested against has no reference counterpart, so it is
+    # tied to the oracle here: weights exp(s - lse) rebuilt from it must reproduce the oracle's attention.
+    B, H, N, d = 1, 2, 192, 64
+    q, k, v = make_inputs(31, B, H, N, d)
+    slopes = np.array([-0.25, -0.0625], dtype=np.float32) if alibi else None
+    lse = ob.log_sum_exp_fp64(q, k, causal=causal, window_left=wl, window_right=wr, alibi_slopes=slopes)
+    want = ob.attention(q, k, v, causal=causal, window_left=wl, window_right=wr, alibi_slopes=slopes)
+    i, j = np.arange(N)[:, None], np.arange(N)[None, :]
+    vis = np.ones((N, N), dtype=bool)
+    if causal:
+        vis &= j <= i
+    if wl >= 0:
+        vis &= (j >= i - wl) & (j <= i + wr)
+    for h in range(H):
+        s = q[0, h].astype(np.float64) @ k[0, h].astype(np.float64).T / np.sqrt(d)
+        if alibi:
+            s -= float(slopes[h]) * np.abs(i - j)
+        w = np.where(vis, np.exp(s - lse[0, h][:, None]), 0.0)
+        assert np.abs(w.sum(axis=1) - 1.0).max() < 1e-12
+        got = w @ v[0, h].astype(np.float64)
+        assert np.abs(got - want[0, h].astype(np.float64)).max() <= 2e-3
+    sub = ob.log_sum_exp_fp64(q, k, causal=causal, window_left=wl, window_right=wr, alibi_slopes=slopes, rows=[0, 5, 191])
+    assert np.array_equal(sub, lse[:, :, [0, 5, 191]])
