@@ -395,6 +395,13 @@ __device__ __forceinline__ uint32_t mapa_u32(uint32_t local_smem_addr, uint32_t 
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// Same arrival with the default (CTA-scope release) ordering, which does not stall the warp for a
+// cluster-scope fence. Enough where what the arrival announces is not generic-proxy memory of the
+// arriving thread: tensor-memory contents (ordered by tcgen05.wait + tcgen05.fence::before_thread_sync),
+// or a TMA write into this CTA's shared memory that this CTA's own tensor core will read.
+__device__ __forceinline__ void mbar_arrive_peer(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 // wait on a local mbarrier whose arrivals may come from the peer CTA (cluster-scope acquire), bounded
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
   uint32_t ok;

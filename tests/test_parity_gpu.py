@@ -158,10 +158,12 @@ def test_edge_shapes_and_windows(pkg, ob, kernel, N, d, causal, wl, wr):
     (512, False, -1, -1), (1024, True, -1, -1), (1000, True, -1, -1), (333, False, -1, -1), (1024, True, 256, -1),
     (700, False, 100, 50), (2048, True, 1024, -1), (129, True, -1, -1),
 ])
-def test_cta_pair_kernel(pkg, ob, N, causal, wl, wr):
-    """The cta_group::2 variant (two CTAs share every K/V tile; head_dim 128 only), flash_forward_ex(kernel=2)."""
+@pytest.mark.parametrize("kernel", [2, 3])
+def test_cta_pair_kernels(pkg, ob, kernel, N, causal, wl, wr):
+    """The cta_group::2 variants (two CTAs share every K/V tile; head_dim 128 only), flash_forward_ex(kernel=2 or 3):
+    2 = four q tiles per item, 3 = one q tile per CTA with the scores computed two kv tiles ahead."""
     q, k, v = make_inputs(N * 3 + 1, 2, 3, N, 128)
-    got = run_gpu(pkg, q, k, v, causal, wl, wr, kernel=2)
+    got = run_gpu(pkg, q, k, v, causal, wl, wr, kernel=kernel)
     want = ob.attention(q, k, v, causal=causal, window_left=wl, window_right=wr)
     assert_close(ob, got, want)
     ref = run_gpu(pkg, q, k, v, causal, wl, wr, kernel=0)
