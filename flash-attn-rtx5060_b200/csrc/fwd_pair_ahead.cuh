@@ -8,14 +8,18 @@
 //
 // Tensor memory per CTA: S_a [0,128), S_b [128,256), O [256,384), P_a [384,448), P_b [448,512).
 // With two score buffers and P in columns of its own, S(t+2) = Q K(t+2)^T depends only on the
-// softmax threads having READ S(t), not on P(t)V(t): the tensor pipe computes scores two tiles
-// ahead of the softmax, and the only serial chain left is the softmax itself. Every hand-off that
+// softmax threads having READ S(t), not on P(t)V(t): the tensor pipe computes scores two to three
+// tiles ahead of the P V products, and the only serial chain left is the softmax itself. Every hand-off that
 // crosses the pair (P ready, S buffer free) therefore has a full softmax tile of slack.
 //
 // Tiles of the whole item list of a cluster are numbered t = 0, 1, ...; tile t uses score buffer,
 // P buffer and alpha slot t & 1, K ring slot 2t and V ring slot 2t + 1 (mod kStages).
-// Roles per CTA (384 threads): warps 0-3 softmax (thread = q row), 4-7 correction + epilogue,
-// warp 8 tensor-core issuer (even CTA) / "my half has landed" relay (odd CTA), warp 9 TMA producer.
+// Roles per CTA (512 threads): warps 0-3 and 4-7 are two softmax groups (thread = q row in both) that
+// take the kv tiles alternately (group w owns the tiles with t & 1 == w), so that the TMEM loads, stores
+// and waits of one tile overlap the exponentials of the next; the reference max of a row travels from
+// tile to tile through shared memory, each group keeps a partial row sum, and the epilogue adds the two.
+// Warps 8-11 correction + epilogue; in the even CTA warp 12 issues the score products and warp 14 the P V
+// products for the pair, in the odd CTA warp 12 forwards "my half has landed"; warp 13 TMA producer.
 // No multicast TMA is used. Work items are assigned statically (serpentine over the cost-ordered
 // list), so the two CTAs need no run-time agreement on the next item.
 #pragma once
@@ -41,23 +45,24 @@ namespace fa {
 
 struct AheadCfg {
   static constexpr int D = 128;
-  static constexpr int kThreads = 384;
+  static constexpr int kThreads = 512;
   static constexpr int kQTileBytes = kBlockM * D * 2;   // 32 KiB, two 16 KiB panels
   static constexpr int kSlotBytes = 16384;              // half a K tile (64 keys x 128) or half a V tile (128 keys x 64)
   static constexpr int kKPanelBytes = 64 * kPanel * 2;  // 8 KiB: 64 keys x 128 B
-  static constexpr int kStages = 10;
+  static constexpr int kStages = 8;  // even: a ring slot then always holds the same kind of tile (K or V), so each of the two issuing warps sees every phase of the slots it waits on
   static constexpr int kOffQ = 0;                                  // two Q buffers (item parity)
   static constexpr int kOffKV = 2 * kQTileBytes;
-  static constexpr int kOffAlpha = kOffKV + kStages * kSlotBytes;  // float[2][128], by t & 1
-  static constexpr int kOffRowSum = kOffAlpha + 2 * kBlockM * 4;   // float[2][128], by item parity
-  static constexpr int kOffBars = kOffRowSum + 2 * kBlockM * 4;
-  static constexpr int kNumBars = 20 + 3 * kStages;
+  static constexpr int kOffAlpha = kOffKV + kStages * kSlotBytes;  // float[4][128], by t & 3
+  static constexpr int kOffRowMax = kOffAlpha + 4 * kBlockM * 4;   // float[2][128], by t & 1: reference max after tile t
+  static constexpr int kOffRowSum = kOffRowMax + 2 * kBlockM * 4;  // float[2 item parity][2 groups][2: sum, max][128]
+  static constexpr int kOffBars = kOffRowSum + 8 * kBlockM * 4;
+  static constexpr int kNumBars = 40 + 3 * kStages;
   static constexpr int kOffMisc = kOffBars + kNumBars * 8;
   static constexpr int kSmemBytes = kOffMisc + 16;
   static constexpr uint32_t kTmemCols = 512;
   static constexpr uint32_t kColS = 0, kColO = 256, kColP = 384;  // S buffer b at kColS + 128 b, P buffer b at kColP + 64 b
   static constexpr float kLazyLog2 = 8.f;
-  static constexpr int kRegSoftmax = 232, kRegCorr = 104, kRegMisc = 80;
+  static constexpr int kRegSoftmax = 168, kRegCorr = 96, kRegMisc = 80;
 };
 
 struct AheadGeom {
@@ -123,7 +128,7 @@ struct AheadCursor {
 };
 
 template <bool kAlibi>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(512, 1)
 fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapKh,
                       const __grid_constant__ CUtensorMap mapVh, const FwdParams p) {
   using Cfg = AheadCfg;
@@ -143,6 +148,7 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   uint8_t* sQ = smem + Cfg::kOffQ;
   uint8_t* sKV = smem + Cfg::kOffKV;
   float* sAlpha = reinterpret_cast<float*>(smem + Cfg::kOffAlpha);
+  float* sRowMax = reinterpret_cast<float*>(smem + Cfg::kOffRowMax);
   float* sRowSum = reinterpret_cast<float*>(smem + Cfg::kOffRowSum);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBars);
   uint64_t* q_full = bars;            // [2] own TMA -> issuer / relay                    (by item parity)
@@ -152,17 +158,19 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   uint64_t* s_free = bars + 8;        // [2] even CTA only: softmax warps of BOTH CTAs have read S -> issuer
   uint64_t* p_full = bars + 10;       // [2] even CTA only: softmax + correction warps of BOTH CTAs -> issuer
   uint64_t* p_free = bars + 12;       // [2] issuer (multicast): P(t) V(t) has completed -> own softmax, correction
-  uint64_t* alpha_ready = bars + 14;  // [2] own softmax -> own correction
-  uint64_t* l_ready = bars + 16;      // own softmax -> own correction (once per item)
-  uint64_t* o_full = bars + 17;       // issuer (multicast) -> own correction (once per item)
-  uint64_t* o_empty = bars + 18;      // even CTA only: correction warps of BOTH CTAs have read O -> issuer
-  uint64_t* kv_full = bars + 20;                       // [kStages] own TMA -> issuer / relay
-  uint64_t* kv_empty = bars + 20 + Cfg::kStages;       // [kStages] issuer (multicast) -> own TMA
-  uint64_t* kv_peer = bars + 20 + 2 * Cfg::kStages;    // [kStages] even CTA only: the odd CTA's half has landed
+  uint64_t* l_ready = bars + 18;      // [2] own softmax group -> own correction (once per item and group)
+  uint64_t* o_full = bars + 15;       // issuer (multicast) -> own correction (once per item)
+  uint64_t* o_empty = bars + 16;      // even CTA only: correction warps of BOTH CTAs have read O -> issuer
+  uint64_t* m_ready = bars + 20;      // [2][4] softmax warp q of the group owning tile t -> warp q of the other group
+  uint64_t* e_done = bars + 28;       // [2][4] same pairing: "my exponentials of tile t are done", the MUFU is yours
+  uint64_t* alpha_ready = bars + 36;  // [4] own softmax -> own correction (by t & 3)
+  uint64_t* kv_full = bars + 40;                       // [kStages] own TMA -> issuer / relay
+  uint64_t* kv_empty = bars + 40 + Cfg::kStages;       // [kStages] issuer (multicast) -> own TMA
+  uint64_t* kv_peer = bars + 40 + 2 * Cfg::kStages;    // [kStages] even CTA only: the odd CTA's half has landed
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  if (warp == 8) {
+  if (warp == 12) {
     tmem_alloc(tmem_slot, Cfg::kTmemCols);  // each CTA allocates all of its own TMEM: same base in both
     tmem_relinquish();
   }
@@ -176,9 +184,14 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       mbar_init(&s_free[b], 8);   // 4 softmax warps of each CTA
       mbar_init(&p_full[b], 16);  // 4 softmax + 4 correction warps of each CTA
       mbar_init(&p_free[b], 1);
-      mbar_init(&alpha_ready[b], 4);
     }
-    mbar_init(l_ready, 4);
+    for (int i = 0; i < 4; ++i) mbar_init(&alpha_ready[i], 4);
+    for (int i = 0; i < 8; ++i) {
+      mbar_init(&m_ready[i], 1);
+      mbar_init(&e_done[i], 1);
+    }
+    mbar_init(&l_ready[0], 4);
+    mbar_init(&l_ready[1], 4);
     mbar_init(o_full, 1);
     mbar_init(o_empty, 8);  // 4 correction warps of each CTA
     for (int i = 0; i < Cfg::kStages; ++i) {
@@ -189,7 +202,7 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     *abort_flag = misaligned ? 1 : 0;
     fence_mbar_init();
   }
-  if (warp == 9 && lane == 0) {
+  if (warp == 13 && lane == 0) {
     prefetch_tensormap(&mapQ);
     prefetch_tensormap(&mapKh);
     prefetch_tensormap(&mapVh);
@@ -210,13 +223,20 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
 
   if (misaligned) {
     // swizzled tiles need a 1024-byte aligned base; nothing was issued, fall through to the common exit
-  } else if (warp < 4) {
+  } else if (warp < 8) {
     // =====================================================================================
-    // softmax: thread = q row of this CTA's tile, kv tiles in sequence
+    // softmax: group w = warp / 4 owns the kv tiles with t & 1 == w; thread = q row
     // =====================================================================================
     reg_inc<Cfg::kRegSoftmax>();
+    const uint32_t w = static_cast<uint32_t>(warp >> 2);
     const int row_l = tid & 127;
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32u;
+    const uint32_t tS = tmem_addr(tmem_base, lane_base, Cfg::kColS + 128u * w);
+    const uint32_t tP = tmem_addr(tmem_base, lane_base, Cfg::kColP + 64u * w);
+    uint64_t* m_mine = &m_ready[w * 4 + (warp & 3)];          // I publish the reference max of my tiles here
+    uint64_t* m_other = &m_ready[(w ^ 1u) * 4 + (warp & 3)];  // the other group's warp of the same rows
+    uint64_t* e_mine = &e_done[w * 4 + (warp & 3)];
+    uint64_t* e_other = &e_done[(w ^ 1u) * 4 + (warp & 3)];
     const float sl2 = kAlibi ? 1.f : p.scale_log2;
     const uint64_t scale2 = f2_pack(sl2, sl2);
     uint32_t t = 0, n_item = 0;
@@ -230,29 +250,34 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       const int row = g.r0 + row_l;
       float slope_l2 = 0.f;
       if (kAlibi) slope_l2 = p.alibi_slopes[g.bh % p.heads] * 1.4426950408889634f;
-      float m_run = -INFINITY;  // true running max of the raw scores
-      float m_used = 0.f;       // max the exponentials are currently taken against
-      float l_run = 0.f;
+      // This group's share of the row: sum of exponentials taken against m_known, over its own tiles.
+      float m_known = 0.f;
+      float l_part = 0.f;
       for (int j = g.lo; j < g.hi; ++j, ++t) {
-        const uint32_t b = t & 1u, ph = (t >> 1) & 1u;
-        const uint32_t tS = tmem_addr(tmem_base, lane_base, Cfg::kColS + 128u * b);
-        const uint32_t tP = tmem_addr(tmem_base, lane_base, Cfg::kColP + 64u * b);
+        if ((t & 1u) != w) continue;
+        const uint32_t ph = (t >> 1) & 1u;
         FA_AP(0);
-        if (!mbar_wait_warp(&s_full[b], ph, abort_flag)) { ok = false; break; }
+        if (!mbar_wait_warp(&s_full[w], ph, abort_flag)) { ok = false; break; }
         tc_fence_after();
         FA_AP(1);
 #ifdef FA_AHEAD_FAKE  // bring-up only: the load + tensor pipeline of the pair without the softmax work
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive_peer(s_free_even[b]);
-        if (!mbar_wait_warp(&p_free[b], ph ^ 1u, abort_flag)) { ok = false; break; }
-        sAlpha[b * kBlockM + row_l] = 1.f;
+        if (lane == 0) mbar_arrive_peer(s_free_even[w]);
+        if (t > 0 && !mbar_wait_warp(m_other, ((t - 1u) >> 1) & 1u, abort_flag)) { ok = false; break; }
         __syncwarp();
-        if (lane == 0) { mbar_arrive(&alpha_ready[b]); mbar_arrive_peer(p_full_even[b]); }
-        l_run = 1.f;
+        if (lane == 0) mbar_arrive(m_mine);
+        if (t > 0 && !mbar_wait_warp(e_other, ((t - 1u) >> 1) & 1u, abort_flag)) { ok = false; break; }
+        if (lane == 0) mbar_arrive(e_mine);
+        if (!mbar_wait_warp(&p_free[w], ph ^ 1u, abort_flag)) { ok = false; break; }
+        sAlpha[(t & 3u) * kBlockM + row_l] = 1.f;
+        __syncwarp();
+        if (lane == 0) { mbar_arrive(&alpha_ready[t & 3u]); mbar_arrive_peer(p_full_even[w]); }
+        l_part = 0.5f;
         continue;
 #endif
         const int kv0 = j * kBlockN;
+        const bool first = (j == g.lo);
         // One body, instantiated twice: tiles cut by a mask boundary (or by the end of the sequence, or lying
         // wholly outside this CTA's visible range, since the item's kv range is the union over the pair)
         // take the per-element predicate and MUFU-only exponentials, all others carry none of that code.
@@ -271,7 +296,7 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           // the scores are in registers: the buffer may take S(t + 2)
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive_peer(s_free_even[b]);
+          if (lane == 0) mbar_arrive_peer(s_free_even[w]);
           FA_AP(2);
           float sc[kBlockN];
 #pragma unroll
@@ -295,7 +320,7 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             for (int c = 0; c < kBlockN; ++c)
               if (c < c_lo || c > c_hi) sc[c] = -INFINITY;
           }
-          float mx0 = m_run, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+          float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
           for (int c = 0; c < kBlockN; c += 8) {
             mx0 = max3(mx0, sc[c], sc[c + 1]);
@@ -303,26 +328,44 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             mx2 = max3(mx2, sc[c + 4], sc[c + 5]);
             mx3 = max3(mx3, sc[c + 6], sc[c + 7]);
           }
-          const float m_new = max3(mx0, mx1, fmaxf(mx2, mx3));
-          // Lazy rescale, branch-free (as in the one-CTA kernel): the reference max moves only when the true
-          // max has grown by more than kLazyLog2 or when no finite score was seen before.
-          const bool fresh = (m_run == -INFINITY);
-          const bool move = fresh || (m_new - m_used) * sl2 > Cfg::kLazyLog2;
-          const float m_next = move ? ((m_new == -INFINITY) ? 0.f : m_new) : m_used;
-          float alpha = ex2_approx((m_used - m_next) * sl2);
-          alpha = fresh ? 1.f : alpha;
-          m_used = m_next;
-          m_run = m_new;
-          // P(t - 2) V(t - 2) has completed: its P buffer and alpha slot (read by the correction warps before
-          // they let that product start) may be overwritten.
+          const float m_tile = max3(mx0, mx1, fmaxf(mx2, mx3));
           FA_AP(3);
-          if (!mbar_wait_warp(&p_free[b], ph ^ 1u, abort_flag)) return false;
-          FA_AP(4);
-          sAlpha[b * kBlockM + row_l] = alpha;
+          // Reference max after the previous tile, from the group that owns it. Every publication is waited
+          // for, also across item boundaries (where its value is not used), so the two groups take strict
+          // turns on these barriers. NaN marks "no finite score seen in this row so far".
+          float m_prev = __int_as_float(0x7fc00000);
+          if (t > 0) {
+            if (!mbar_wait_warp(m_other, ((t - 1u) >> 1) & 1u, abort_flag)) return false;
+            if (!first) m_prev = sRowMax[(w ^ 1u) * kBlockM + row_l];
+          }
+          // Lazy rescale: the reference max moves only when this tile's max exceeds it by more than kLazyLog2
+          // (P then stays below 2^8, well inside fp16), or when the row had no finite score before.
+          const bool fresh = !(m_prev == m_prev);
+          const bool move = fresh ? (m_tile != -INFINITY) : ((m_tile - m_prev) * sl2 > Cfg::kLazyLog2);
+          const float m_ref = move ? m_tile : m_prev;  // stays NaN while the row is still empty
+          sRowMax[w * kBlockM + row_l] = m_ref;
           __syncwarp();
-          if (lane == 0) mbar_arrive(&alpha_ready[b]);
-
-          const float neg_ms = -m_used * sl2;
+          if (lane == 0) mbar_arrive(m_mine);
+          const bool empty = !(m_ref == m_ref);
+          const float m_use = empty ? 0.f : m_ref;     // exponentials of an empty row: exp2(-inf - 0) = 0
+          float alpha = (fresh || empty) ? 1.f : ex2_approx((m_prev - m_ref) * sl2);
+          // my partial sum moves from the reference I last used to the current one
+          const float shift = (l_part > 0.f) ? ex2_approx((m_known - m_use) * sl2) : 0.f;
+          m_known = m_use;
+          // The alpha slot is reused every fourth tile: the correction warps read alpha(t - 4) before P(t - 4) V(t - 4)
+          // started, and this group waited for that product to complete during its previous tile.
+          sAlpha[(t & 3u) * kBlockM + row_l] = alpha;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&alpha_ready[t & 3u]);
+          FA_AP(4);
+          // The two warps that share an SM sub-partition (same rows, one per group) take turns on its MUFU:
+          // without this the groups settle into running their exponentials at the same time at half rate
+          // each, and their loads, maxima and waits at the same time too, so nothing overlaps.
+          if (t > 0 && !mbar_wait_warp(e_other, ((t - 1u) >> 1) & 1u, abort_flag)) return false;
+          FA_AP(7);
+          // P(t - 2) V(t - 2) has completed: its P buffer may be overwritten.
+          if (!mbar_wait_warp(&p_free[w], ph ^ 1u, abort_flag)) return false;
+          const float neg_ms = -m_use * sl2;
           const uint64_t negms2 = f2_pack(neg_ms, neg_ms);
           uint64_t lsum_a = 0ull, lsum_b = 0ull;
           uint32_t pk0[32], pk1[32];
@@ -330,15 +373,17 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           exp_half_tile<!kMasked>(sc, scale2, negms2, pk0, lsum_a, lsum_b);
           tmem_st32(tP + 0, pk0);
           exp_half_tile<!kMasked>(sc + 64, scale2, negms2, pk1, lsum_a, lsum_b);
-          tmem_st32(tP + 32, pk1);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(e_mine);
           float l0, l1;
           f2_unpack(f2_add(lsum_a, lsum_b), l0, l1);
-          l_run = l_run * alpha + (l0 + l1);
+          l_part = l_part * shift + (l0 + l1);
           FA_AP(5);
+          tmem_st32(tP + 32, pk1);
           tmem_wait_st();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive_peer(p_full_even[b]);  // the whole P tile is in TMEM
+          if (lane == 0) mbar_arrive_peer(p_full_even[w]);  // the whole P tile is in TMEM
           FA_AP(6);
           return true;
         };
@@ -347,13 +392,15 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         if (!ok) break;
       }
       if (!ok) break;
-      sRowSum[(n_item & 1u) * kBlockM + row_l] = l_run;
+      float* part = sRowSum + ((n_item & 1u) * 2u + w) * 2u * kBlockM;
+      part[row_l] = l_part;
+      part[kBlockM + row_l] = m_known;
       __syncwarp();
-      if (lane == 0) mbar_arrive(l_ready);
+      if (lane == 0) mbar_arrive(&l_ready[w]);
       ++n_item;
     }
     FA_AP_STORE(blockIdx.x == 0 && tid == 0, 0);
-  } else if (warp < 8) {
+  } else if (warp < 12) {
     // =====================================================================================
     // correction + epilogue for this CTA's rows
     // =====================================================================================
@@ -361,6 +408,7 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     const int row_l = tid & 127;
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32u;
     const uint32_t tO = tmem_addr(tmem_base, lane_base, Cfg::kColO);
+    const float sl2 = kAlibi ? 1.f : p.scale_log2;
     uint32_t t = 0, n_item = 0;
     bool ok = true;
     for (int round = 0; ok; ++round) {
@@ -370,11 +418,12 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       const AheadGeom g = decode_ahead_item(item, p, rank);
       for (int j = g.lo; j < g.hi && ok; ++j, ++t) {
         const uint32_t b = t & 1u, ph = (t >> 1) & 1u;
-        if (!mbar_wait_warp(&alpha_ready[b], ph, abort_flag)) { ok = false; break; }
-        const float alpha = sAlpha[b * kBlockM + row_l];
+        if (!mbar_wait_warp(&alpha_ready[t & 3u], (t >> 2) & 1u, abort_flag)) { ok = false; break; }
+        const float alpha = sAlpha[(t & 3u) * kBlockM + row_l];
+        // O may be rescaled only between P(t-1) V(t-1) and P(t) V(t): wait for the former to complete. The wait is
+        // taken for every tile, needed or not, so that every phase of these barriers is observed in turn.
+        if (t > 0 && !mbar_wait_warp(&p_free[b ^ 1u], ((t - 1u) >> 1) & 1u, abort_flag)) { ok = false; break; }
         if (j > g.lo && __any_sync(0xffffffffu, alpha != 1.f)) {
-          // O may be rescaled only between P(t-1) V(t-1) and P(t) V(t): wait for the former to complete
-          if (!mbar_wait_warp(&p_free[b ^ 1u], ((t - 1u) >> 1) & 1u, abort_flag)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
           for (int c = 0; c < D / 32; ++c) {
@@ -393,8 +442,16 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         if (lane == 0) mbar_arrive_peer(p_full_even[b]);
       }
       if (!ok) break;
-      if (!mbar_wait_warp(l_ready, n_item & 1u, abort_flag)) break;
-      const float l = sRowSum[(n_item & 1u) * kBlockM + row_l];
+      if (!mbar_wait_warp(&l_ready[0], n_item & 1u, abort_flag)) break;
+      if (!mbar_wait_warp(&l_ready[1], n_item & 1u, abort_flag)) break;
+      // Row sum = the two groups' partial sums brought to the reference O was accumulated against, which is
+      // the one the owner of the last tile ended with.
+      const uint32_t own = (t - 1u) & 1u;
+      const float* part_own = sRowSum + ((n_item & 1u) * 2u + own) * 2u * kBlockM;
+      const float* part_oth = sRowSum + ((n_item & 1u) * 2u + (own ^ 1u)) * 2u * kBlockM;
+      const float l_oth = part_oth[row_l];
+      float l = part_own[row_l];
+      if (l_oth > 0.f) l += l_oth * ex2_approx((part_oth[kBlockM + row_l] - part_own[kBlockM + row_l]) * sl2);
       if (!mbar_wait_warp(o_full, n_item & 1u, abort_flag)) break;
       ++n_item;
       tc_fence_after();
@@ -427,10 +484,9 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     }
   } else {
     reg_dec<Cfg::kRegMisc>();
-    if (warp == 8 && rank == 0) {
+    if ((warp == 12 || warp == 14) && rank == 0) {
       // ===================================================================================
-      // tensor-core issuer of the pair (even CTA). Two cursors walk the same tile stream: the
-      // score cursor runs two tiles ahead of the P V cursor, across item boundaries.
+      // tensor-core issuers of the pair (even CTA)
       // ===================================================================================
       constexpr uint32_t idesc_qk = umma_idesc_f16(2 * kBlockM, kBlockN, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_f16(2 * kBlockM, D, 0, 1);
@@ -505,26 +561,24 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         return true;
       };
 
-      AheadCursor cs, cp;
-      cs.start(p, rank, cluster_id, num_clusters);
-      cp = cs;
-      for (int i = 0; i < 2 && ok && cs.valid; ++i) {  // scores of the first two tiles
-        ok = issue_scores(cs);
-        cs.advance(p, rank, cluster_id, num_clusters);
-      }
-      while (ok && cp.valid) {
-        // S(t + 2) first: it only waits for the softmax to have READ S(t), which happens early in
-        // tile t, so it completes while that softmax is still running.
-        if (cs.valid) {
-          ok = issue_scores(cs);
-          cs.advance(p, rank, cluster_id, num_clusters);
-          if (!ok) break;
+      // Two issuing warps, one per kind of product: S(t) = Q K(t)^T needs "K(t) has landed" and "S(t - 2) has been
+      // read", P(t) V(t) needs "V(t) has landed" and "P(t) is ready". The two chains share nothing but the tensor
+      // pipe, so neither ever waits behind an instruction of the other that is not ready yet.
+      AheadCursor c;
+      c.start(p, rank, cluster_id, num_clusters);
+      if (warp == 12) {
+        while (ok && c.valid) {
+          ok = issue_scores(c);
+          c.advance(p, rank, cluster_id, num_clusters);
         }
-        ok = issue_pv(cp);
-        cp.advance(p, rank, cluster_id, num_clusters);
+      } else {
+        while (ok && c.valid) {
+          ok = issue_pv(c);
+          c.advance(p, rank, cluster_id, num_clusters);
+        }
       }
-      FA_AP_STORE(blockIdx.x == 0 && lane == 0, 1);
-    } else if (warp == 8 && rank == 1 && lane == 0) {
+      FA_AP_STORE(blockIdx.x == 0 && lane == 0, warp == 12 ? 1 : 2);
+    } else if (warp == 12 && rank == 1 && lane == 0) {
       // ===================================================================================
       // odd CTA: tell the issuer when this CTA's Q tile and K/V halves have landed
       // ===================================================================================
@@ -549,7 +603,7 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           }
         }
       }
-    } else if (warp == 9 && lane == 0) {
+    } else if (warp == 13 && lane == 0) {
       // ===================================================================================
       // TMA producer: own Q tile, own half of every K and V tile
       // ===================================================================================
@@ -591,7 +645,7 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   // touch it.
   cluster_sync_all();
   if (tid == 0 && *abort_flag != 0) atomicExch(p.status, misaligned ? 2 : 1);
-  if (warp == 8) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  if (warp == 12) tmem_dealloc(tmem_base, Cfg::kTmemCols);
 }
 
 }  // namespace fa
