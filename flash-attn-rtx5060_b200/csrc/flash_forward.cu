@@ -17,7 +17,6 @@
 
 #include "../../include/flash_forward_b200.h"
 #include "fwd_params.h"
-#include "fwd_pair.cuh"
 #include "fwd_pair_ahead.cuh"
 #include "fwd_persistent.cuh"
 #include "fwd_serial.cuh"
@@ -67,7 +66,7 @@ struct DeviceState {
   int num_sms = 0;
   int* status = nullptr;  // device words: [0] status, then kSchedSlots pairs of scheduler words
   unsigned next_sched = 0;
-  bool attr_set[14] = {};
+  bool attr_set[12] = {};
 };
 DeviceState g_dev[kMaxDevices];
 
@@ -143,37 +142,14 @@ int launch_serial(DeviceState* s, const CUtensorMap& mq, const CUtensorMap& mk, 
   return FA_OK;
 }
 
-// CTA-pair kernel (head_dim 128): clusters of two CTAs, static serpentine work assignment.
-int launch_pair(DeviceState* s, const void* q, const void* k, const void* v, fa::FwdParams p, cudaStream_t st) {
-  using Cfg = fa::PairCfg;
-  const bool alibi = p.alibi_slopes != nullptr;
-  int rc = alibi ? ensure_smem_attr(s, 7, fa::fwd_pair_kernel<true>, Cfg::kSmemBytes)
-                 : ensure_smem_attr(s, 6, fa::fwd_pair_kernel<false>, Cfg::kSmemBytes);
-  if (rc != FA_OK) return rc;
-  const int quads = (p.seqlen + 4 * fa::kBlockM - 1) / (4 * fa::kBlockM);
-  p.num_q_pairs = quads;  // the pair kernel counts items in quads of q tiles
-  p.num_items = p.bh * quads;
-  CUtensorMap mq, mkh, mvh;
-  if ((rc = make_map(&mq, q, p.bh, p.seqlen, 128, fa::kBlockM)) != FA_OK) return rc;
-  if ((rc = make_map(&mkh, k, p.bh, p.seqlen, 128, 64)) != FA_OK) return rc;          // half a K tile: 64 keys
-  if ((rc = make_map(&mvh, v, p.bh, p.seqlen, 128, fa::kBlockN, 1)) != FA_OK) return rc;  // half a V tile: one 64-wide panel
-  int clusters = s->num_sms / 2;
-  if (p.num_items < clusters) clusters = p.num_items;
-  if (alibi) fa::fwd_pair_kernel<true><<<2 * clusters, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mkh, mvh, p);
-  else fa::fwd_pair_kernel<false><<<2 * clusters, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mkh, mvh, p);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return fail_cuda("launch fwd_pair_kernel", e);
-  return FA_OK;
-}
-
 // CTA-pair kernel with scores computed two tiles ahead (head_dim 128): one q tile per CTA, items are
 // pairs of q tiles as in the one-CTA kernel, assigned statically to the clusters.
 int launch_pair_ahead(DeviceState* s, const void* q, const void* k, const void* v, const fa::FwdParams& p,
                       cudaStream_t st) {
   using Cfg = fa::AheadCfg;
   const bool alibi = p.alibi_slopes != nullptr;
-  int rc = alibi ? ensure_smem_attr(s, 13, fa::fwd_pair_ahead_kernel<true>, Cfg::kSmemBytes)
-                 : ensure_smem_attr(s, 12, fa::fwd_pair_ahead_kernel<false>, Cfg::kSmemBytes);
+  int rc = alibi ? ensure_smem_attr(s, 7, fa::fwd_pair_ahead_kernel<true>, Cfg::kSmemBytes)
+                 : ensure_smem_attr(s, 6, fa::fwd_pair_ahead_kernel<false>, Cfg::kSmemBytes);
   if (rc != FA_OK) return rc;
   CUtensorMap mq, mkh, mvh;
   if ((rc = make_map(&mq, q, p.bh, p.seqlen, 128, fa::kBlockM)) != FA_OK) return rc;
@@ -371,9 +347,8 @@ static int forward_impl(const void* q, const void* k, const void* v, void* o, in
        reinterpret_cast<uintptr_t>(o)) & 15)
     return fail(FA_INVALID_ARG, "tensor pointers must be 16-byte aligned");
   if ((long long)batch * heads > 0x7fffffffLL) return fail(FA_INVALID_ARG, "batch*heads overflows int");
-  if (kernel < 0 || kernel > 3)
-    return fail(FA_INVALID_ARG, "kernel must be 0 (default), 1 (serial), 2 (CTA pair) or 3 (CTA pair, scores ahead)");
-  if (kernel >= 2 && head_dim != 128) return fail(FA_UNSUPPORTED, "the CTA-pair kernels need head_dim 128");
+  if (kernel < 0 || kernel > 2) return fail(FA_INVALID_ARG, "kernel must be 0 (default), 1 (serial) or 2 (CTA pair)");
+  if (kernel == 2 && head_dim != 128) return fail(FA_UNSUPPORTED, "the CTA-pair kernel needs head_dim 128");
   if (!(softmax_scale == softmax_scale)) return fail(FA_INVALID_ARG, "softmax_scale is NaN");
 
   DeviceState* s = nullptr;
@@ -423,8 +398,7 @@ static int forward_impl(const void* q, const void* k, const void* v, void* o, in
   if ((rc = make_map(&mv, v, bh, seqlen, head_dim, fa::kBlockN)) != FA_OK) return rc;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (kernel == 2) return launch_pair(s, q, k, v, p, st);
-  if (kernel == 3) return launch_pair_ahead(s, q, k, v, p, st);
+  if (kernel == 2) return launch_pair_ahead(s, q, k, v, p, st);
   if (kernel == 1) {
     return head_dim == 64 ? launch_serial<64>(s, mq, mk, mv, p, st) : launch_serial<128>(s, mq, mk, mv, p, st);
   }

@@ -23,7 +23,6 @@
 // No multicast TMA is used. Work items are assigned statically (serpentine over the cost-ordered
 // list), so the two CTAs need no run-time agreement on the next item.
 #pragma once
-#include "fwd_pair.cuh"
 #include "fwd_params.h"
 #include "fwd_persistent.cuh"
 #include "ptx.cuh"
@@ -62,7 +61,7 @@ struct AheadCfg {
   static constexpr uint32_t kTmemCols = 512;
   static constexpr uint32_t kColS = 0, kColO = 256, kColP = 384;  // S buffer b at kColS + 128 b, P buffer b at kColP + 64 b
   static constexpr float kLazyLog2 = 8.f;
-  static constexpr int kRegSoftmax = 168, kRegCorr = 96, kRegMisc = 80;
+  static constexpr int kRegSoftmax = 184, kRegCorr = 80, kRegMisc = 64;  // 8*32*184 + 4*32*80 + 4*32*64 = 64 Ki registers
 };
 
 struct AheadGeom {
@@ -93,6 +92,15 @@ __device__ __forceinline__ AheadGeom decode_ahead_item(int item, const FwdParams
   g.lo = kv_tile_begin(a0, p.window_left);
   g.hi = kv_tile_end(last, wr, p.seqlen);
   return g;
+}
+
+// i-th item of cluster c out of G clusters: a serpentine over the cost-ordered list, so that every
+// cluster gets a similar mix of long and short items. Returns -1 when the list is exhausted for
+// this round, -2 when all rounds are done.
+__device__ __forceinline__ int pair_item(int round, int c, int G, int num_items) {
+  if (round * G >= num_items) return -2;
+  const int idx = round * G + ((round & 1) ? (G - 1 - c) : c);
+  return idx < num_items ? idx : -1;
 }
 
 // Position in the cluster's tile stream: item after item, kv tile after kv tile.
@@ -417,7 +425,7 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       if (item < 0) continue;
       const AheadGeom g = decode_ahead_item(item, p, rank);
       for (int j = g.lo; j < g.hi && ok; ++j, ++t) {
-        const uint32_t b = t & 1u, ph = (t >> 1) & 1u;
+        const uint32_t b = t & 1u;
         if (!mbar_wait_warp(&alpha_ready[t & 3u], (t >> 2) & 1u, abort_flag)) { ok = false; break; }
         const float alpha = sAlpha[(t & 3u) * kBlockM + row_l];
         // O may be rescaled only between P(t-1) V(t-1) and P(t) V(t): wait for the former to complete. The wait is

@@ -391,48 +391,14 @@ __device__ __forceinline__ uint32_t mapa_u32(uint32_t local_smem_addr, uint32_t 
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
   return r;
 }
-// arrival on an mbarrier of any CTA of the cluster (address from mapa_u32)
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-// Same arrival with the default (CTA-scope release) ordering, which does not stall the warp for a
-// cluster-scope fence. Enough where what the arrival announces is not generic-proxy memory of the
-// arriving thread: tensor-memory contents (ordered by tcgen05.wait + tcgen05.fence::before_thread_sync),
-// or a TMA write into this CTA's shared memory that this CTA's own tensor core will read.
+// Arrival on an mbarrier of any CTA of the cluster (address from mapa_u32), with the default (CTA-scope
+// release) ordering. A cluster-scope release (.release.cluster) stalls the arriving warp for a fence of
+// several hundred cycles, which cost a third of the pair kernel's throughput; it is not needed where what
+// the arrival announces is not generic-proxy memory of the arriving thread: tensor-memory contents
+// (ordered by tcgen05.wait + tcgen05.fence::before_thread_sync), or a TMA write into this CTA's shared
+// memory that this CTA's own tensor core will read.
 __device__ __forceinline__ void mbar_arrive_peer(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-// wait on a local mbarrier whose arrivals may come from the peer CTA (cluster-scope acquire), bounded
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred P;\n"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, P;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait_cluster(bar, parity)) return true;
-  long long t0 = clock64();
-  uint32_t polls = 0;
-  while (!mbar_try_wait_cluster(bar, parity)) {
-    if ((++polls & 1023u) == 0) {
-      if (*abort_flag != 0) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
-        *abort_flag = 1;
-        return false;
-      }
-    }
-  }
-  return true;
-}
-__device__ __forceinline__ bool mbar_wait_cluster_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  return __all_sync(0xffffffffu, mbar_wait_cluster(bar, parity, abort_flag));
 }
 // One instruction for both CTAs of the pair (issued by one thread of the even-ranked CTA): M = 256
 // rows (128 per CTA, each from its own shared memory / TMEM at the same offsets), B split along N

@@ -158,10 +158,10 @@ def test_edge_shapes_and_windows(pkg, ob, kernel, N, d, causal, wl, wr):
     (512, False, -1, -1), (1024, True, -1, -1), (1000, True, -1, -1), (333, False, -1, -1), (1024, True, 256, -1),
     (700, False, 100, 50), (2048, True, 1024, -1), (129, True, -1, -1),
 ])
-@pytest.mark.parametrize("kernel", [2, 3])
-def test_cta_pair_kernels(pkg, ob, kernel, N, causal, wl, wr):
-    """The cta_group::2 variants (two CTAs share every K/V tile; head_dim 128 only), flash_forward_ex(kernel=2 or 3):
-    2 = four q tiles per item, 3 = one q tile per CTA with the scores computed two kv tiles ahead."""
+def test_cta_pair_kernel(pkg, ob, N, causal, wl, wr):
+    """The cta_group::2 kernel (two CTAs share every K/V tile, one q tile per CTA, scores computed two kv tiles
+    ahead; head_dim 128 only), flash_forward_ex(kernel=2)."""
+    kernel = 2
     q, k, v = make_inputs(N * 3 + 1, 2, 3, N, 128)
     got = run_gpu(pkg, q, k, v, causal, wl, wr, kernel=kernel)
     want = ob.attention(q, k, v, causal=causal, window_left=wl, window_right=wr)
@@ -169,6 +169,30 @@ def test_cta_pair_kernels(pkg, ob, kernel, N, causal, wl, wr):
     ref = run_gpu(pkg, q, k, v, causal, wl, wr, kernel=0)
     mx, mean, nans = ob.abs_error(got, ref)
     assert nans == 0 and mx <= 2e-3
+
+
+@pytest.mark.parametrize("B,H,N,causal,wl", [
+    (1, 150, 512, True, -1),    # 300 items on 74 clusters: several short items (2 and 4 kv tiles) per cluster
+    (3, 7, 2176, True, 300),    # windowed: items with odd numbers of kv tiles, ragged last pair
+    (1, 40, 4096, False, -1),   # 16 long items of equal length per head
+])
+def test_cta_pair_kernel_many_items(pkg, ob, B, H, N, causal, wl):
+    """The pair kernel streams the items of a cluster back to back (scores of the next item are issued while the
+    last tiles of the current one are still in the softmax); every hand-off that is counted per item or per tile
+    must survive short items. Two runs each, against the oracle on sampled heads and against the default kernel
+    on everything."""
+    import torch
+
+    q, k, v = make_inputs(4000 + N + H, B, H, N, 128)
+    tq, tk, tv = (torch.from_numpy(a).cuda() for a in (q, k, v))
+    ref = pkg.attention_forward(tq, tk, tv, causal=causal, window_left=wl, kernel=0)
+    for _ in range(2):
+        got = pkg.attention_forward(tq, tk, tv, causal=causal, window_left=wl, kernel=2)
+        pkg.check(torch.cuda.current_stream().cuda_stream)
+        assert float((got.float() - ref.float()).abs().max()) <= 2e-3
+    heads = [0, H // 2, H - 1]
+    want = ob.attention(q[:1, heads], k[:1, heads], v[:1, heads], causal=causal, window_left=wl, window_right=-1)
+    assert_close(ob, got[:1, heads].cpu().numpy(), want)
 
 
 def exact_attention(q, k, v, scale, causal):
