@@ -25,10 +25,12 @@
 #include "fwd_params.h"
 #include "ptx.cuh"
 
+// Registers per thread after setmaxnreg: 8 softmax warps, 4 correction warps, 4 others; the three
+// numbers must satisfy 256 * softmax + 128 * correction + 128 * others <= 65536.
 #ifndef FA_REG_SOFTMAX
-#define FA_REG_SOFTMAX 168
-#define FA_REG_CORR 96
-#define FA_REG_MISC 80
+#define FA_REG_SOFTMAX 176
+#define FA_REG_CORR 88
+#define FA_REG_MISC 72
 #endif
 
 // Of every 8 pairs of scores, this many pairs take their 2^x from a polynomial on the FMA pipe
