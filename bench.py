@@ -39,12 +39,12 @@ OTHER_CONFIGS = [
     dict(name="C3", B=2, H=32, N=8192, d=128, causal=True, wl=-1, wr=-1),
     dict(name="C4", B=4, H=16, N=16384, d=128, causal=True, wl=1024, wr=-1),
 ]
-# 12 heads of the workload's own per-head shape (two head groups of 6): the case the DRAM-traffic capture runs on;
-# traffic per head carries over to the full workload because heads are scheduled in groups of 6 there too.
+# 12 heads of the workload's own per-head shape (three head groups of 4): the case the DRAM-traffic capture runs on;
+# traffic per head carries over to the full workload because heads are scheduled in groups of 4 there too.
 TRAFFIC_CASE = dict(name="C5s", B=1, H=12, N=32768, d=128, causal=True, wl=-1, wr=-1)
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of TRAFFIC_CASE under ncu (677.5 MB + 86.9 MB for 12
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of TRAFFIC_CASE under ncu (442.9 MB + 88.3 MB for 12
 # heads; profiles/fwd_persistent_d128_causal_N32768_traffic.md), per head. Algorithmic bytes per head are 33.6 MB.
-TRAFFIC_BYTES_PER_HEAD = (677522944 + 86895104) / 12
+TRAFFIC_BYTES_PER_HEAD = (442907648 + 88302336) / 12
 METRIC = "fwd attention TFLOP/s (whole job; FLOPs = 4*B*H*N^2*d, halved for causal)"
 FALLBACK_TFLOPS = 1590.0  # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
 

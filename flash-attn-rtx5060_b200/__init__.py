@@ -35,6 +35,7 @@ EXPORTS = (
     "flash_forward_last_error",
     "flash_forward_flops",
     "flash_forward_kv_range",
+    "flash_forward_head_group",
     "flash_forward_shutdown",
 )
 
@@ -84,6 +85,8 @@ def lib():
     ip = ctypes.POINTER(ctypes.c_int)
     L.flash_forward_kv_range.argtypes = [i, i, i, i, i, i, ip, ip, ip]
     L.flash_forward_kv_range.restype = i
+    L.flash_forward_head_group.argtypes = [i, i, i, i, i, i, i]
+    L.flash_forward_head_group.restype = i
     L.flash_forward_shutdown.argtypes = []
     L.flash_forward_shutdown.restype = i
     _lib = L
@@ -150,6 +153,12 @@ def kv_range(seqlen, is_causal, window_left, window_right, row_begin, row_end):
     if rc != FA_OK:
         _raise(rc)
     return a.value, b.value, c.value
+
+
+def head_group(batch_heads, seqlen, head_dim, is_causal=False, window_left=-1, window_right=-1, num_sms=148):
+    """Heads per scheduling group the default kernel uses for this shape (host logic)."""
+    return lib().flash_forward_head_group(batch_heads, seqlen, head_dim, int(bool(is_causal)), window_left, window_right,
+                                          num_sms)
 
 
 def run_flash_attention(B, N, S, d, Q, K, V, O, L=None, M=None, Is_dropout=False, Is_causal=False, Is_local=False,

@@ -297,6 +297,35 @@ int launch_persistent_noalloc(NoAllocState* s, const CUtensorMap& mq, const CUte
 
 }  // namespace
 
+// Heads per scheduling group of the persistent kernel. Without a mask all items cost the same and head-major
+// order (1) shares K/V best. With a causal mask or a window the item costs differ, and interleaving the heads of
+// a group pair-major keeps the tail short. Three measured constraints (B200): the K and V rows that a group
+// keeps live (the whole head, or the window span) should stay within ~64 MB (the 126 MB L2 holds two copies of
+// what both dies read: the long-context workload read K/V from DRAM 2.2 times with 96 MB in flight, 1.5 times
+// with 64 MB, 1.1 times with 48 MB, at the same speed; the 8192-row config is 0.6 % faster with 64 MB than
+// with 48); a group needs about two items per CTA to balance; and the groups must be of even size (64 heads in
+// groups of 12 leave a last group of 4 heads, too few items for 148 CTAs: -4 %).
+static int pick_head_group(int bh, int seqlen, int head_dim, int causal, int window_left, int window_right,
+                           int num_q_pairs, int num_sms) {
+  if (!causal && window_left < 0 && window_right < 0) return 1;
+  const int wr = causal ? 0 : window_right;
+  long long span = seqlen;
+  if (window_left >= 0 && wr >= 0) {
+    span = (long long)window_left + wr + 2 * fa::kBlockM;
+    if (span > seqlen) span = seqlen;
+  }
+  const double span_bytes = 4.0 * (double)span * head_dim;  // K and V rows, fp16
+  int grp_l2 = (int)(64.0 * 1024 * 1024 / span_bytes);
+  const int grp_bal = (2 * num_sms + num_q_pairs - 1) / num_q_pairs;
+  int grp = grp_l2 < 16 ? grp_l2 : 16;
+  if (grp < grp_bal) grp = grp_bal;
+  if (grp > 16) grp = 16;
+  if (grp < 1) grp = 1;
+  if (grp > bh) grp = bh;
+  const int groups = (bh + grp - 1) / grp;
+  return (bh + groups - 1) / groups;
+}
+
 extern "C" {
 
 const char* flash_forward_last_error(void) { return g_err; }
@@ -315,6 +344,14 @@ double flash_forward_flops(int batch, int heads, int seqlen, int head_dim, int i
     if (hi >= lo) pairs += hi - lo + 1;
   }
   return 4.0 * bh * pairs * d;
+}
+
+int flash_forward_head_group(int batch_heads, int seqlen, int head_dim, int is_causal, int window_left,
+                             int window_right, int num_sms) {
+  if (batch_heads <= 0 || seqlen <= 0 || (head_dim != 64 && head_dim != 128) || num_sms <= 0) return 0;
+  const int pairs = (seqlen + 2 * fa::kBlockM - 1) / (2 * fa::kBlockM);
+  return pick_head_group(batch_heads, seqlen, head_dim, is_causal ? 1 : 0, window_left < 0 ? -1 : window_left,
+                         window_right < 0 ? -1 : window_right, pairs, num_sms);
 }
 
 int flash_forward_kv_range(int seqlen, int is_causal, int window_left, int window_right, int row_begin,
@@ -377,19 +414,10 @@ static int forward_impl(const void* q, const void* k, const void* v, void* o, in
   p.num_q_pairs = (seqlen + 2 * fa::kBlockM - 1) / (2 * fa::kBlockM);
   if ((long long)bh * p.num_q_pairs > 0x7fffffffLL) return fail(FA_INVALID_ARG, "too many work items");
   p.num_items = bh * p.num_q_pairs;
-  {  // Heads per scheduling group. Without a mask all items cost the same and head-major order (1)
-     // shares K/V best. With a causal mask or a window the item costs differ, and interleaving the
-     // heads of a group pair-major keeps the tail short; the group's K and V (2 * N * d * 2 bytes per
-     // head) are kept within ~96 MB of L2. Both choices were measured on B200.
-    const double head_bytes = 4.0 * seqlen * head_dim;
-    int grp = (int)(96.0 * 1024 * 1024 / head_bytes);
-    p.head_group = grp < 1 ? 1 : (grp > 16 ? 16 : grp);
-    if (!p.causal && p.window_left < 0 && p.window_right < 0) p.head_group = 1;
-    if (const char* e = getenv("FA_HEAD_GROUP")) {  // tuning knob for experiments
-      const int v = atoi(e);
-      if (v > 0) p.head_group = v;
-    }
-    if (p.head_group > bh) p.head_group = bh;
+  p.head_group = pick_head_group(bh, seqlen, head_dim, p.causal, p.window_left, p.window_right, p.num_q_pairs, s->num_sms);
+  if (const char* e = getenv("FA_HEAD_GROUP")) {  // tuning knob for experiments
+    const int v = atoi(e);
+    if (v > 0) p.head_group = v < bh ? v : bh;
   }
 
   CUtensorMap mq, mk, mv;
@@ -611,13 +639,7 @@ int flash_forward_noalloc(const void* q, const void* k, const void* v, void* o, 
   p.sched = words + 2;
   p.num_q_pairs = pairs;
   p.num_items = bh * pairs;
-  {
-    const double head_bytes = 4.0 * seqlen * head_dim;
-    int grp = (int)(96.0 * 1024 * 1024 / head_bytes);
-    p.head_group = grp < 1 ? 1 : (grp > 16 ? 16 : grp);
-    if (!p.causal && p.window_left < 0 && p.window_right < 0) p.head_group = 1;
-    if (p.head_group > bh) p.head_group = bh;
-  }
+  p.head_group = pick_head_group(bh, seqlen, head_dim, p.causal, p.window_left, p.window_right, pairs, s->num_sms);
 
   CUtensorMap mq, mk, mv;
   if ((rc = make_map(&mq, q, bh, seqlen, head_dim, fa::kBlockM)) != FA_OK) return rc;

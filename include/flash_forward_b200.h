@@ -124,6 +124,12 @@ int run_flash_attention_c(int B, int N, int S, int d, void* Q, void* K, void* V,
                           int Is_dropout, int Is_causal, int Is_local, int Has_alibi, int window_size,
                           float* alibi_slopes, float dropout_prob, void* states);
 
+/* Heads per scheduling group that the default kernel would use for batch_heads = batch*heads problems of this
+ * shape on a GPU with num_sms SMs (1 = head-major order). Host logic only, for tests and tuning; the reference
+ * schedules q tiles in natural order (src/flash_forward.h:43-64) and has no such notion. 0 on bad arguments. */
+int flash_forward_head_group(int batch_heads, int seqlen, int head_dim, int is_causal, int window_left,
+                             int window_right, int num_sms);
+
 /* Message for the last non-OK status returned on the calling thread ("" if none). */
 const char* flash_forward_last_error(void);
 

@@ -116,3 +116,23 @@ def test_tile_plan_matches_brute_force(pkg, N, causal, wl, wr):
             if blk.shape[1] < 128 or not blk.all():
                 want_masked += 1
         assert masked == want_masked, (r0, masked, want_masked)
+
+
+def test_head_group_policy(pkg):
+    # no mask: head-major order
+    assert pkg.head_group(64, 8192, 128) == 1
+    # BASELINE configs 2-5 (causal / causal + window), 148 SMs
+    assert pkg.head_group(64, 2048, 64, True) == 16
+    assert pkg.head_group(64, 8192, 128, True) == 16      # 64 MB / 4 MB per head
+    assert pkg.head_group(40, 8192, 128, True) == 14      # 16 would leave a last group of 8: three even groups instead
+    assert pkg.head_group(64, 16384, 128, True, 1024) == 16  # only the window span stays live
+    assert pkg.head_group(512, 32768, 128, True) == 4
+    assert pkg.head_group(0, 128, 64) == 0 and pkg.head_group(4, 128, 96) == 0
+    for bh in (1, 2, 3, 7, 12, 64, 100, 512):
+        for N in (128, 1000, 4096, 32768, 131072):
+            for d in (64, 128):
+                for wl in (-1, 0, 300):
+                    g = pkg.head_group(bh, N, d, True, wl)
+                    assert 1 <= g <= min(16, bh)
+                    groups = -(-bh // g)
+                    assert bh - (groups - 1) * g >= g - (groups - 1)  # the last group is not a stub
