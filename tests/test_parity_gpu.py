@@ -140,6 +140,33 @@ def test_large_configs_sampled(pkg, ob, B, H, N, d, causal, wl):
     assert (out2.float() - 2 * out.float()).abs().max().item() <= 2.0 ** -23
 
 
+def test_very_long_sequence_and_very_many_heads(pkg, ob):
+    """The two ends of the work-item space: one head of 131072 rows (512 q pairs, a 64 MB K/V working set, 1024 kv
+    tiles for the last rows) and 6000 heads of 256 rows (one item per head, the dynamic work counter hands out
+    ~5850 items). Sampled rows against the oracle for the long one, everything for the many."""
+    import torch
+
+    g = torch.Generator(device="cuda").manual_seed(131)
+    N, d = 131072, 128
+    q, k, v = (torch.randn((1, 1, N, d), generator=g, device="cuda", dtype=torch.float16) for _ in range(3))
+    out = pkg.attention_forward(q, k, v, causal=True)
+    pkg.check(torch.cuda.current_stream().cuda_stream)
+    rows = np.unique(np.concatenate([np.arange(0, 130), np.arange(65530, 65540), np.arange(N - 64, N),
+                                     np.random.default_rng(2).integers(0, N, 24)])).astype(np.int32)
+    hq, hk, hv, ho = (x[0, 0].cpu().numpy() for x in (q, k, v, out))
+    want = ob.attention_rows(hq, hk, hv, rows, causal=True, window_left=-1, window_right=-1)
+    assert_close(ob, ho[rows], want)
+    assert torch.isfinite(out).all()
+    del q, k, v, out
+
+    q, k, v = make_inputs(6000, 6000, 1, 256, 64)
+    got = run_gpu(pkg, q, k, v, True, 100, -1)
+    want = ob.attention(q, k, v, causal=True, window_left=100, window_right=-1)
+    # 98 M outputs, the early causal rows are averages of a handful of N(0,1) values: some exceed 2, where one
+    # fp16 ulp is already 1.95e-3 (two ulps were seen once in 98 M), so the bound on the maximum is two ulps there
+    assert_close(ob, got, want, max_abs=4e-3)
+
+
 @pytest.mark.parametrize("kernel", [0, 1])
 @pytest.mark.parametrize("N,d,causal,wl,wr", [
     (1, 64, False, -1, -1), (5, 128, True, -1, -1), (127, 64, True, -1, -1), (129, 128, False, -1, -1),
