@@ -12,8 +12,8 @@
 // tiles ahead of the P V products, and the only serial chain left is the softmax itself. Every hand-off that
 // crosses the pair (P ready, S buffer free) therefore has a full softmax tile of slack.
 //
-// Tiles of the whole item list of a cluster are numbered t = 0, 1, ...; tile t uses score buffer,
-// P buffer and alpha slot t & 1, K ring slot 2t and V ring slot 2t + 1 (mod kStages).
+// Tiles of the whole item list of a cluster are numbered t = 0, 1, ...; tile t uses score buffer and
+// P buffer t & 1, alpha slot t & 3, K ring slot 2t and V ring slot 2t + 1 (mod kStages).
 // Roles per CTA (512 threads): warps 0-3 and 4-7 are two softmax groups (thread = q row in both) that
 // take the kv tiles alternately (group w owns the tiles with t & 1 == w), so that the TMEM loads, stores
 // and waits of one tile overlap the exponentials of the next; the reference max of a row travels from
@@ -48,7 +48,9 @@ struct AheadCfg {
   static constexpr int kQTileBytes = kBlockM * D * 2;   // 32 KiB, two 16 KiB panels
   static constexpr int kSlotBytes = 16384;              // half a K tile (64 keys x 128) or half a V tile (128 keys x 64)
   static constexpr int kKPanelBytes = 64 * kPanel * 2;  // 8 KiB: 64 keys x 128 B
-  static constexpr int kStages = 8;  // even: a ring slot then always holds the same kind of tile (K or V), so each of the two issuing warps sees every phase of the slots it waits on
+  // even: a ring slot then always holds the same kind of tile (K or V), so each of the two issuing warps sees
+  // every phase of the slots it waits on
+  static constexpr int kStages = 8;
   static constexpr int kOffQ = 0;                                  // two Q buffers (item parity)
   static constexpr int kOffKV = 2 * kQTileBytes;
   static constexpr int kOffAlpha = kOffKV + kStages * kSlotBytes;  // float[4][128], by t & 3
