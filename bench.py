@@ -188,7 +188,7 @@ def run_reference(args):
     return 0
 
 
-def time_config(pkg, torch, cfg, heads, iters, warmup, stream):
+def time_config(pkg, torch, cfg, heads, iters, warmup, stream, kernel=0):
     """Device-resident timing of one configuration on the current GPU (heads = this rank's slab)."""
     N, d = cfg["N"], cfg["d"]
     g = torch.Generator(device="cuda")
@@ -196,7 +196,8 @@ def time_config(pkg, torch, cfg, heads, iters, warmup, stream):
     q, k, v = (torch.randn((1, heads, N, d), generator=g, device="cuda", dtype=torch.float16) for _ in range(3))
     o = torch.empty_like(q)
     args = (q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), 1, heads, N, d)
-    kw = dict(is_causal=cfg["causal"], window_left=cfg["wl"], window_right=cfg["wr"], stream=stream.cuda_stream)
+    kw = dict(is_causal=cfg["causal"], window_left=cfg["wl"], window_right=cfg["wr"], stream=stream.cuda_stream,
+              kernel=kernel)
     for _ in range(warmup):
         pkg.flash_forward(*args, **kw)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -221,6 +222,8 @@ def main():
     ap.add_argument("--heads-per-gpu", type=int, default=0, help="override the slab size (debugging only)")
     ap.add_argument("--case", default="", help="profiling aid: time only this smaller configuration (C1..C4) on one "
                     "GPU, device-resident, and print a short JSON line that is not a benchmark line")
+    ap.add_argument("--kernel", type=int, default=0, help="with --case only: 0 default kernel, 2 CTA-pair kernel "
+                    "(head_dim 128 cases)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
@@ -243,8 +246,8 @@ def main():
 
     if args.case:
         c = next(x for x in OTHER_CONFIGS + [TRAFFIC_CASE] if x["name"] == args.case)
-        ms, fl_c, _ = time_config(pkg, torch, c, c["B"] * c["H"], args.steps, args.warmup, stream)
-        print(json.dumps(dict(case=c["name"], ms=ms, tflops=fl_c / (ms * 1e-3) / 1e12, steps=args.steps,
+        ms, fl_c, _ = time_config(pkg, torch, c, c["B"] * c["H"], args.steps, args.warmup, stream, args.kernel)
+        print(json.dumps(dict(case=c["name"], kernel=args.kernel, ms=ms, tflops=fl_c / (ms * 1e-3) / 1e12, steps=args.steps,
                               note="profiling aid, not a benchmark line")))
         return 0
 
