@@ -312,7 +312,7 @@ def main():
         parity = dict(rows=int(rows.size), max_abs=mx, mean_abs=mean, nan=nans, ok=bool(nans == 0 and mx <= 2e-3 and mean <= 2e-4))
 
     # ---- end to end: host buffers through the C ABI, copies inside the timed region ----------
-    chunk = min(32, heads)
+    chunk = min(8, heads)  # heads per upload/kernel/download stage: 8 measured 3 % faster than 32 (shorter fill and drain)
     ws_bytes = pkg.host_workspace_bytes(N, d, chunk)
     hq, hk, hv = (torch.empty((1, heads, N, d), dtype=torch.float16, pin_memory=True) for _ in range(3))
     ho = torch.empty((1, heads, N, d), dtype=torch.float16, pin_memory=True)
