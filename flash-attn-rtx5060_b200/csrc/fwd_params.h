@@ -46,20 +46,23 @@ struct FwdParams {
 // per-element predicate.
 __host__ __device__ inline int eff_window_right(int causal, int wr) { return causal ? 0 : wr; }
 
-__host__ __device__ inline int kv_tile_begin(int r0, int wl) {
+// `bn` is the number of keys per kv tile (128 in the kernels that keep one score tile per q tile, 64 in the
+// kernel that double-buffers its score tiles).
+__host__ __device__ inline int kv_tile_begin(int r0, int wl, int bn = kBlockN) {
   if (wl < 0) return 0;
   int lo = r0 - wl;
-  return lo <= 0 ? 0 : lo / kBlockN;
+  return lo <= 0 ? 0 : lo / bn;
 }
-__host__ __device__ inline int kv_tile_end(int r1, int wr_eff, int seqlen) {  // exclusive
+__host__ __device__ inline int kv_tile_end(int r1, int wr_eff, int seqlen, int bn = kBlockN) {  // exclusive
   int hi = seqlen - 1;
   if (wr_eff >= 0 && r1 + wr_eff < hi) hi = r1 + wr_eff;
-  return hi / kBlockN + 1;
+  return hi / bn + 1;
 }
-__host__ __device__ inline bool kv_tile_needs_mask(int kv0, int r0, int r1, int wl, int wr_eff, int seqlen) {
-  if (kv0 + kBlockN > seqlen) return true;                      // ragged tail
-  if (wr_eff >= 0 && kv0 + kBlockN - 1 > r0 + wr_eff) return true;  // right / causal boundary
-  if (wl >= 0 && kv0 < r1 - wl) return true;                    // left window boundary
+__host__ __device__ inline bool kv_tile_needs_mask(int kv0, int r0, int r1, int wl, int wr_eff, int seqlen,
+                                                   int bn = kBlockN) {
+  if (kv0 + bn > seqlen) return true;                          // ragged tail
+  if (wr_eff >= 0 && kv0 + bn - 1 > r0 + wr_eff) return true;  // right / causal boundary
+  if (wl >= 0 && kv0 < r1 - wl) return true;                   // left window boundary
   return false;
 }
 

@@ -28,8 +28,8 @@
 // Registers per thread after setmaxnreg: 8 softmax warps, 4 correction warps, 4 others; the three
 // numbers must satisfy 256 * softmax + 128 * correction + 128 * others <= 65536.
 #ifndef FA_REG_SOFTMAX
-#define FA_REG_SOFTMAX 176
-#define FA_REG_CORR 88
+#define FA_REG_SOFTMAX 184
+#define FA_REG_CORR 72
 #define FA_REG_MISC 72
 #endif
 
@@ -39,9 +39,22 @@
 #define FA_EMU_PAIRS 0
 #endif
 
+
 // Optional timeline capture for kernel bring-up (compile with -DFA_TRACE and pass a dbg buffer):
 // CTA 0 records clock64() stamps of its first work item, 8 stamps per (role, iteration).
-#ifdef FA_TRACE
+#if defined(FA_TRACE3)
+// boundary trace: the last 44 rounds of CTA 0's first work item land in rows 0..43, the first 20 rounds of its
+// second item in rows 44..63
+#define FA_TR(cond, role, iter, slot)                                                                  \
+  do {                                                                                                 \
+    if (blockIdx.x == 0 && p.dbg != nullptr && (cond)) {                                               \
+      int it_ = -1;                                                                                    \
+      if (n_items == 1) { it_ = (iter) - (g.hi_all - g.lo_all - 40); if (it_ >= 44) it_ = -1; }        \
+      else if (n_items == 2 && (iter) >= 0 && (iter) < 20) it_ = 44 + (iter);                          \
+      if (it_ >= 0 && it_ < 64) reinterpret_cast<long long*>(p.dbg)[((role) * 64 + it_) * 8 + (slot)] = clock64(); \
+    }                                                                                                  \
+  } while (0)
+#elif defined(FA_TRACE)
 #define FA_TR(cond, role, iter, slot)                                                             \
   do {                                                                                            \
     if (blockIdx.x == 0 && item == 0 && p.dbg != nullptr && (cond) && (iter) >= 0 && (iter) < 64) \
@@ -60,7 +73,7 @@
 #define FA_TM(role, iter, slot)                                        \
   do {                                                                 \
     const uint32_t t_now = static_cast<uint32_t>(clock());             \
-    prof_acc[((role) == 5 ? 8 : 0) + (slot)] += t_now - prof_last;     \
+    prof_acc[((role) == 14 ? 8 : 0) + (slot)] += t_now - prof_last;     \
     prof_last = t_now;                                                 \
   } while (0)
 #else
@@ -82,7 +95,8 @@ struct PersistentCfg {
   static constexpr int kOffBars = kOffRowSum + 2 * kBlockM * 4;
   static constexpr int kNumBars = 20 + 2 * kStages;
   static constexpr int kOffMisc = kOffBars + kNumBars * 8;
-  static constexpr int kSmemBytes = kOffMisc + 16;  // TMEM base, abort flag, two work-item slots
+  static constexpr int kOffGeom = kOffMisc + 16;     // TMEM base, abort flag (+ 8 spare bytes)
+  static constexpr int kSmemBytes = kOffGeom + 2 * 64;  // two work-item slots: the item's decoded geometry and its id
   static constexpr uint32_t kTmemCols = 512;
   static constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
   // softmax threshold (in log2 units) below which a larger row max does not trigger a rescale
@@ -102,6 +116,7 @@ struct ItemGeom {
 // the longest) q pair to the first. CTAs claim items in this order from a global counter, so CTAs
 // that run together read the same few heads, and the items handed out last are the cheapest ones
 // of the last group: the tail stays short.
+template <int BN = kBlockN>
 __device__ __forceinline__ ItemGeom decode_item(int item, const FwdParams& p) {
   ItemGeom g;
   const int per_group = p.head_group * p.num_q_pairs;
@@ -122,8 +137,8 @@ __device__ __forceinline__ ItemGeom decode_item(int item, const FwdParams& p) {
       g.lo[s] = g.hi[s] = 0;
     } else {
       g.r1[s] = min(g.r0[s] + kBlockM, p.seqlen) - 1;
-      g.lo[s] = kv_tile_begin(g.r0[s], p.window_left);
-      g.hi[s] = kv_tile_end(g.r1[s], wr, p.seqlen);
+      g.lo[s] = kv_tile_begin(g.r0[s], p.window_left, BN);
+      g.hi[s] = kv_tile_end(g.r1[s], wr, p.seqlen, BN);
       g.lo_all = min(g.lo_all, g.lo[s]);
       g.hi_all = max(g.hi_all, g.hi[s]);
     }
@@ -174,6 +189,26 @@ __device__ __forceinline__ void exp_half_tile(const float* sc, uint64_t scale2, 
   }
 }
 
+// Same for 32 scores (16 pairs) -> the first 16 words of pk.
+template <bool kAllowPoly>
+__device__ __forceinline__ void exp_quarter_tile(const float* sc, uint64_t scale2, uint64_t negms2, uint32_t* pk,
+                                                 uint64_t& lsum_a, uint64_t& lsum_b) {
+#pragma unroll
+  for (int c = 0; c < 16; ++c) {
+    float x0, x1, e0, e1;
+    f2_unpack(f2_fma(f2_pack(sc[2 * c], sc[2 * c + 1]), scale2, negms2), x0, x1);
+    if (kAllowPoly && (c % 8) < FA_EMU_PAIRS) {
+      exp2_poly_pair(x0, x1, e0, e1);
+    } else {
+      e0 = ex2_approx(x0);
+      e1 = ex2_approx(x1);
+    }
+    if (c & 1) lsum_b = f2_add(lsum_b, f2_pack(e0, e1));
+    else lsum_a = f2_add(lsum_a, f2_pack(e0, e1));
+    pk[c] = pack_f16x2(e0, e1);
+  }
+}
+
 template <int D, bool kAlibi, bool kLse = false>
 __global__ void __launch_bounds__(512, 1)
 fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
@@ -209,7 +244,8 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   uint64_t* kv_empty = bars + 20 + Cfg::kStages;  // [kStages] MMA -> TMA
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* s_item = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [2]
+  // [2][16]: ItemGeom of the published item in words 0..11, its id (-1: no more items) in word 12
+  volatile int* s_geom = reinterpret_cast<volatile int*>(smem + Cfg::kOffGeom);
   constexpr uint32_t kItemReaders = 13;  // 8 softmax warps + 4 correction warps + the MMA warp
 
   if (warp == 12) {
@@ -251,12 +287,17 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   const int wl = p.window_left;
   const int wr = eff_window_right(p.causal, p.window_right);
 
-  // Every consuming warp reads the k-th work item id from slot k & 1 once the producer has
-  // published it, and releases the slot. -1 ends the walk (also after a give-up).
-  auto take_item = [&](uint32_t& n_items) -> int {
+  // Every consuming warp reads the k-th work item (id and geometry, decoded once by the producer) from slot
+  // k & 1 once the producer has published it, and releases the slot. -1 ends the walk (also after a give-up).
+  auto take_item = [&](uint32_t& n_items, ItemGeom& g) -> int {
     const uint32_t slot = n_items & 1u;
     if (!mbar_wait_warp(&item_full[slot], (n_items >> 1) & 1u, abort_flag)) return -1;
-    const int it = s_item[slot];
+    const volatile int* w = s_geom + slot * 16;
+    const int it = w[12];
+    g.bh = w[0]; g.pair = w[1];
+    g.r0[0] = w[2]; g.r0[1] = w[3]; g.r1[0] = w[4]; g.r1[1] = w[5];
+    g.lo[0] = w[6]; g.lo[1] = w[7]; g.hi[0] = w[8]; g.hi[1] = w[9];
+    g.lo_all = w[10]; g.hi_all = w[11];
     __syncwarp();
     if (lane == 0) mbar_arrive(&item_empty[slot]);
     ++n_items;
@@ -280,9 +321,9 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     uint32_t n_items = 0;
     bool ok = true;
     while (ok) {
-      const int item = take_item(n_items);
+      ItemGeom g;
+      const int item = take_item(n_items, g);
       if (item < 0) break;
-      const ItemGeom g = decode_item(item, p);
       const int q_r0 = s ? g.r0[1] : g.r0[0];
       const int q_r1 = s ? g.r1[1] : g.r1[0];
       const int j_lo = s ? g.lo[1] : g.lo[0];
@@ -298,7 +339,13 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         if (!mbar_wait_warp(&s_full[s], n_s & 1, abort_flag)) { ok = false; break; }
         ++n_s;
         tc_fence_after();
-        FA_TR(row_l == 0, s, j - j_lo, 0);
+#ifdef FA_TRACE2
+        if (blockIdx.x == 0 && warp == 0 && lane == 0 && p.dbg != nullptr && n_s < 1300) {
+          long long* o = reinterpret_cast<long long*>(p.dbg) + 3 * (n_s - 1);
+          o[0] = clock64(); o[1] = item; o[2] = j;
+        }
+#endif
+        FA_TR(lane == 0, warp, j - j_lo, 0);
 #ifdef FA_FAKE_SOFTMAX  // bring-up only: measures the load + tensor pipeline without the softmax work
         if (FA_FAKE_SOFTMAX > 0) {
           const long long t_end = clock64() + FA_FAKE_SOFTMAX;
@@ -306,13 +353,15 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         }
         sAlpha[s * kBlockM + row_l] = 1.f;
         __syncwarp();
-        if (lane == 0) { mbar_arrive(&alpha_ready[s]); mbar_arrive(&p_full[s]); mbar_arrive(&p_full2[s]); }
+        if (lane == 0) { if (j != j_lo) mbar_arrive(&alpha_ready[s]); mbar_arrive(&p_full[s]); mbar_arrive(&p_full2[s]); }
         l_run = 1.f;
         continue;
 #endif
         const int kv0 = j * kBlockN;
-        // One body, instantiated twice: tiles cut by a mask boundary (or by the end of the sequence) take
-        // the per-element predicate and MUFU-only exponentials, all others carry none of that code.
+        // One body, instantiated twice: tiles cut by a mask boundary (or by the end of the sequence) take the
+        // per-element predicate, all others carry none of that code. (Blanking a cut tile in tensor memory first
+        // and sharing one body saved 10 KB of instructions but made every tile 4 % slower: the body then
+        // starts behind a merge point instead of directly behind the wait.)
         auto tile_body = [&](auto masked_tag) {
           constexpr bool kMasked = decltype(masked_tag)::value;
           uint32_t r0[32], r1[32], r2[32], r3[32];
@@ -325,7 +374,7 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           tmem_ld_fence(r1);
           tmem_ld_fence(r2);
           tmem_ld_fence(r3);
-          FA_TR(row_l == 0, s, j - j_lo, 1);
+          FA_TR(lane == 0, warp, j - j_lo, 1);
           float sc[kBlockN];
   #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -348,6 +397,16 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             for (int c = 0; c < kBlockN; ++c)
               if (c < c_lo || c > c_hi) sc[c] = -INFINITY;
           }
+          // The exponentials of the first 32 keys are taken against the reference the previous tile left while
+          // the row max of this tile is still being reduced: nearly always the reference stays where it is (lazy
+          // rescale), so the max leaves the critical path. When a row of the warp does move its reference
+          // (always on the first tile of an item), the 32 exponentials are taken again.
+          uint64_t lsum_a = 0ull, lsum_b = 0ull;
+          uint32_t pk0[32], pk1[32];
+          {
+            const float neg_ms0 = -m_used * sl2;
+            exp_quarter_tile<!kMasked>(sc, scale2, f2_pack(neg_ms0, neg_ms0), pk0, lsum_a, lsum_b);
+          }
           float mx0 = m_run, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
   #pragma unroll
           for (int c = 0; c < kBlockN; c += 8) {
@@ -357,33 +416,38 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             mx3 = max3(mx3, sc[c + 6], sc[c + 7]);
           }
           const float m_new = max3(mx0, mx1, fmaxf(mx2, mx3));
-          // Lazy rescale, branch-free: the reference max moves only when the true max has grown by more
-          // than kLazyLog2 (P then stays below 2^8, well inside fp16) or when no finite score was seen
-          // before; otherwise alpha = 2^0 = 1 exactly.
+          // The reference moves when the true max has grown past it by more than kLazyLog2 (P then stays below
+          // 2^8, well inside fp16), and always on the first tile that shows a finite score: the reference then IS
+          // the row max, so the largest term of the row is exactly 1 in fp16 (a row with a single visible key
+          // returns that key's V bit for bit).
           const bool fresh = (m_run == -INFINITY);
           const bool move = fresh || (m_new - m_used) * sl2 > Cfg::kLazyLog2;
-          const float m_next = move ? ((m_new == -INFINITY) ? 0.f : m_new) : m_used;
-          float alpha = ex2_approx((m_used - m_next) * sl2);
-          alpha = fresh ? 1.f : alpha;
-          m_used = m_next;
+          float alpha = 1.f;
           m_run = m_new;
+          if (__any_sync(0xffffffffu, move)) {
+            const float m_next = move ? ((m_new == -INFINITY) ? 0.f : m_new) : m_used;
+            alpha = fresh ? 1.f : ex2_approx((m_used - m_next) * sl2);
+            m_used = m_next;
+            lsum_a = 0ull;
+            lsum_b = 0ull;
+            const float neg_ms1 = -m_used * sl2;
+            exp_quarter_tile<!kMasked>(sc, scale2, f2_pack(neg_ms1, neg_ms1), pk0, lsum_a, lsum_b);
+          }
+          // (no hand-over on the first tile of an item: there is nothing to rescale yet, and the correction warps
+          // may still be in the previous item's epilogue)
           sAlpha[s * kBlockM + row_l] = alpha;
           __syncwarp();
-          if (lane == 0) mbar_arrive(&alpha_ready[s]);
-          FA_TR(row_l == 0, s, j - j_lo, 2);
-
+          if (lane == 0 && j != j_lo) mbar_arrive(&alpha_ready[s]);
+          FA_TR(lane == 0, warp, j - j_lo, 2);
           const float neg_ms = -m_used * sl2;
           const uint64_t negms2 = f2_pack(neg_ms, neg_ms);
-          uint64_t lsum_a = 0ull, lsum_b = 0ull;
-          uint32_t pk0[32], pk1[32];
-          // masked tiles hold -inf scores, which only the MUFU path maps to 0
-          exp_half_tile<!kMasked>(sc, scale2, negms2, pk0, lsum_a, lsum_b);
+          exp_quarter_tile<!kMasked>(sc + 32, scale2, negms2, pk0 + 16, lsum_a, lsum_b);
           tmem_st32(tS + 0, pk0);
           tmem_wait_st();
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&p_full[s]);  // P of keys 0..63 is in TMEM
-          FA_TR(row_l == 0, s, j - j_lo, 3);
+          FA_TR(lane == 0, warp, j - j_lo, 3);
           exp_half_tile<!kMasked>(sc + 64, scale2, negms2, pk1, lsum_a, lsum_b);
           tmem_st32(tS + 32, pk1);
           float l0, l1;
@@ -396,7 +460,7 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         };
         if (kv_tile_needs_mask(kv0, q_r0, q_r1, wl, wr, N)) tile_body(std::true_type{});
         else tile_body(std::false_type{});
-        FA_TR(row_l == 0, s, j - j_lo, 4);
+        FA_TR(lane == 0, warp, j - j_lo, 4);
       }
       if (!ok) break;
       sRowSum[s * kBlockM + row_l] = l_run;
@@ -417,73 +481,105 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32u;
     uint32_t n_alpha[2] = {0, 0}, n_l[2] = {0, 0}, n_o[2] = {0, 0};
     uint32_t n_items = 0;
+    // The first P.V product of an item overwrites O, so it has to wait until the epilogue of the previous item
+    // has read O. That hand-off is the correction warps' arrival on p_full for the item's first tile; it is made
+    // right after the epilogue (there is nothing to rescale on a first tile), so the next item's first product
+    // does not wait for these warps to come round to it.
+    bool arrived_early[2] = {false, false};
     bool ok = true;
     while (ok) {
-      const int item = take_item(n_items);
+      ItemGeom g;
+      const int item = take_item(n_items, g);
       if (item < 0) break;
-      const ItemGeom g = decode_item(item, p);
-      for (int j = g.lo_all; j < g.hi_all && ok; ++j) {
-#pragma unroll
-        for (int s = 0; s < 2; ++s) {
-          if (j < g.lo[s] || j >= g.hi[s]) continue;
-          if (!mbar_wait_warp(&alpha_ready[s], n_alpha[s] & 1, abort_flag)) { ok = false; break; }
-          ++n_alpha[s];
-          FA_TR(row_l == 0, 2, j - g.lo_all, s * 4 + 0);
-          const float alpha = sAlpha[s * kBlockM + row_l];
-          if (j > g.lo[s] && __any_sync(0xffffffffu, alpha != 1.f)) {
-            tc_fence_after();
-            const uint32_t tO = tmem_addr(tmem_base, lane_base, s == 0 ? Cfg::kColO0 : Cfg::kColO1);
-#pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-              uint32_t r[32];
-              tmem_ld32(tO + c * 32, r);
-              tmem_wait_ld();
-              tmem_ld_fence(r);
-#pragma unroll
-              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-              tmem_st32(tO + c * 32, r);
-            }
-            tmem_wait_st();
-          }
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&p_full[s]);
-          FA_TR(row_l == 0, 2, j - g.lo_all, s * 4 + 1);
-        }
-      }
-      if (!ok) break;
-#pragma unroll
-      for (int s = 0; s < 2; ++s) {
-        if (g.r1[s] < g.r0[s]) continue;
-        if (!mbar_wait_warp(&l_ready[s], n_l[s] & 1, abort_flag)) { ok = false; break; }
+      bool epi_pending[2] = {g.r1[0] >= g.r0[0], g.r1[1] >= g.r0[1]};
+      // O / l -> fp16 -> global for stage s, then the early arrival for the next item's first tile
+      auto epilogue = [&](auto stage_tag) {
+        constexpr int s = decltype(stage_tag)::value;
+        epi_pending[s] = false;
+        if (!mbar_wait_warp(&l_ready[s], n_l[s] & 1, abort_flag)) { ok = false; return; }
         ++n_l[s];
         const float l = sRowSum[s * kBlockM + row_l];
-        if (!mbar_wait_warp(&o_full[s], n_o[s] & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait_warp(&o_full[s], n_o[s] & 1, abort_flag)) { ok = false; return; }
         ++n_o[s];
         tc_fence_after();
+        FA_TR(lane == 0, warp, g.hi_all - g.lo_all - 1, s * 4 + 2);
         const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
         const int row = g.r0[s] + row_l;
         const uint32_t tO = tmem_addr(tmem_base, lane_base, s == 0 ? Cfg::kColO0 : Cfg::kColO1);
         __half* orow = p.O + (static_cast<size_t>(g.bh) * N + row) * D;
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tO + c * 32, r);
+        // 16 columns at a time, the load of the next chunk in flight while this one is converted and stored.
+        // (Rolled up: this path runs once per item and stage, and instructions that are rarely executed are
+        // fetched slowly; unrolling it eightfold made the change-over between items slower, not faster.)
+        uint32_t ra[16], rb[16];
+        tmem_ld16(tO, ra);
+  #pragma unroll 2
+        for (int c = 0; c < D / 16; ++c) {
+          uint32_t (&cur)[16] = (c & 1) ? rb : ra;
+          uint32_t (&nxt)[16] = (c & 1) ? ra : rb;
           tmem_wait_ld();
-          tmem_ld_fence(r);
+          tmem_ld_fence16(cur);
+          if (c + 1 < D / 16) tmem_ld16(tO + (c + 1) * 16, nxt);
           if (row < N) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
+  #pragma unroll
+            for (int i = 0; i < 2; ++i) {
               uint4 v;
-              v.x = pack_f16x2(__uint_as_float(r[i * 8 + 0]) * inv_l, __uint_as_float(r[i * 8 + 1]) * inv_l);
-              v.y = pack_f16x2(__uint_as_float(r[i * 8 + 2]) * inv_l, __uint_as_float(r[i * 8 + 3]) * inv_l);
-              v.z = pack_f16x2(__uint_as_float(r[i * 8 + 4]) * inv_l, __uint_as_float(r[i * 8 + 5]) * inv_l);
-              v.w = pack_f16x2(__uint_as_float(r[i * 8 + 6]) * inv_l, __uint_as_float(r[i * 8 + 7]) * inv_l);
-              *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = v;
+              v.x = pack_f16x2(__uint_as_float(cur[i * 8 + 0]) * inv_l, __uint_as_float(cur[i * 8 + 1]) * inv_l);
+              v.y = pack_f16x2(__uint_as_float(cur[i * 8 + 2]) * inv_l, __uint_as_float(cur[i * 8 + 3]) * inv_l);
+              v.z = pack_f16x2(__uint_as_float(cur[i * 8 + 4]) * inv_l, __uint_as_float(cur[i * 8 + 5]) * inv_l);
+              v.w = pack_f16x2(__uint_as_float(cur[i * 8 + 6]) * inv_l, __uint_as_float(cur[i * 8 + 7]) * inv_l);
+              *reinterpret_cast<uint4*>(orow + c * 16 + i * 8) = v;
             }
           }
         }
+        // O of this stage has been read: let the next item's first product overwrite it
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[s]);
+        arrived_early[s] = true;
+        FA_TR(lane == 0, warp, g.hi_all - g.lo_all - 1, s * 4 + 3);
+      };
+      for (int j = g.lo_all; j < g.hi_all && ok; ++j) {
+        // a stage that has run out of tiles is finished first, while the other stage is still in its softmax
+        if (epi_pending[0] && j >= g.hi[0]) epilogue(std::integral_constant<int, 0>{});
+        if (epi_pending[1] && j >= g.hi[1]) epilogue(std::integral_constant<int, 1>{});
+        if (!ok) break;
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          if (j < g.lo[s] || j >= g.hi[s]) continue;
+          if (j == g.lo[s]) {  // first tile of the item: nothing to rescale, and no factors are handed over
+            const bool done = arrived_early[s];
+            arrived_early[s] = false;
+            if (done) continue;
+          } else {
+            if (!mbar_wait_warp(&alpha_ready[s], n_alpha[s] & 1, abort_flag)) { ok = false; break; }
+            ++n_alpha[s];
+            FA_TR(lane == 0, warp, j - g.lo_all, s * 4 + 0);
+            const float alpha = sAlpha[s * kBlockM + row_l];
+            if (__any_sync(0xffffffffu, alpha != 1.f)) {
+              tc_fence_after();
+              const uint32_t tO = tmem_addr(tmem_base, lane_base, s == 0 ? Cfg::kColO0 : Cfg::kColO1);
+#pragma unroll 1
+              for (int c = 0; c < D / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(tO + c * 32, r);
+                tmem_wait_ld();
+                tmem_ld_fence(r);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                tmem_st32(tO + c * 32, r);
+              }
+              tmem_wait_st();
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&p_full[s]);
+          FA_TR(lane == 0, warp, j - g.lo_all, s * 4 + 1);
+        }
       }
+      if (!ok) break;
+      if (epi_pending[0]) epilogue(std::integral_constant<int, 0>{});
+      if (ok && epi_pending[1]) epilogue(std::integral_constant<int, 1>{});
     }
   } else {
     reg_dec<FA_REG_MISC>();
@@ -509,9 +605,9 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       uint32_t prof_last = static_cast<uint32_t>(clock());
 #endif
       while (ok) {
-        const int item = take_item(n_items);
+        ItemGeom g;
+        const int item = take_item(n_items, g);
         if (item < 0) break;
-        const ItemGeom g = decode_item(item, p);
         // Ring positions are carried along instead of recomputed: (slot_v, par_v) is where V_j lives,
         // (slot_k, par_k) where K_{j+1} lives. Rounds in which both stages have a P.V for tile j and a
         // score tile j+1 ("interior", nearly all of a long sequence) take a branch-free body; the first
@@ -541,13 +637,13 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             const uint32_t colO = (s == 0) ? Cfg::kColO0 : Cfg::kColO1;
             if (act_j) {  // O_s += P_s(j) V_j, in two halves of 64 keys as P arrives
               const uint64_t vdesc = vdesc0 + ((kv_addr + slot_v * Cfg::kTileBytes) >> 4);
-              FA_TM(3, j - g.lo_all + 1, s * 4 + 0);
+              FA_TM(12, j - g.lo_all + 1, s * 4 + 0);
               if (!v_seen && !mbar_wait_warp(&kv_full[slot_v], par_v, abort_flag)) { ok = false; return; }
 #ifndef FA_FAKE_NOWAIT  // (bring-up only: lets the issuer run without the softmax hand-shake)
               if (!mbar_wait_warp(&p_full[s], n_p[s] & 1, abort_flag)) { ok = false; return; }
 #endif
               tc_fence_after();
-              FA_TM(3, j - g.lo_all + 1, s * 4 + 1);
+              FA_TM(12, j - g.lo_all + 1, s * 4 + 1);
               if (elect_one()) {
                 umma_ts(tmem_base + colO, tmem_base + colS, vdesc, idesc_pv, (kInterior || j > g.lo[s]) ? 1u : 0u);
 #pragma unroll
@@ -555,13 +651,13 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                   umma_ts(tmem_base + colO, tmem_base + colS + kk * 8, vdesc + kk * (2048 >> 4), idesc_pv, 1u);
               }
               __syncwarp();
-              FA_TM(3, j - g.lo_all + 1, s * 4 + 2);
+              FA_TM(12, j - g.lo_all + 1, s * 4 + 2);
 #ifndef FA_FAKE_NOWAIT
               if (!mbar_wait_warp(&p_full2[s], n_p[s] & 1, abort_flag)) { ok = false; return; }
 #endif
               ++n_p[s];
               tc_fence_after();
-              FA_TM(3, j - g.lo_all + 1, s * 4 + 3);
+              FA_TM(12, j - g.lo_all + 1, s * 4 + 3);
               if (elect_one()) {
 #pragma unroll
                 for (int kk = 4; kk < 8; ++kk)
@@ -570,7 +666,7 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 if (!kInterior && j + 1 == g.hi[s]) umma_commit(&o_full[s]);
               }
               __syncwarp();
-              FA_TM(5, j - g.lo_all + 1, s * 4 + 0);
+              FA_TM(14, j - g.lo_all + 1, s * 4 + 0);
             }
             if (act_n) {  // S_s = Q_s K_{j+1}^T
               if (!kInterior && j + 1 == g.lo[s]) {
@@ -579,7 +675,7 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
               }
               if (!k_seen && !mbar_wait_warp(&kv_full[slot_k], par_k, abort_flag)) { ok = false; return; }
               tc_fence_after();
-              FA_TM(5, j - g.lo_all + 1, s * 4 + 1);
+              FA_TM(14, j - g.lo_all + 1, s * 4 + 1);
               const uint64_t kdesc = kdesc0 + ((kv_addr + slot_k * Cfg::kTileBytes) >> 4);
               if (elect_one()) {
 #pragma unroll
@@ -592,7 +688,7 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 if (!kInterior && j + 2 == g.hi[s]) umma_commit(&q_empty[s]);
               }
               __syncwarp();
-              FA_TM(5, j - g.lo_all + 1, s * 4 + 2);
+              FA_TM(14, j - g.lo_all + 1, s * 4 + 2);
             }
           }
         };
@@ -628,10 +724,19 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       int next = (static_cast<int>(blockIdx.x) < p.num_items) ? static_cast<int>(blockIdx.x) : -1;
       while (ok) {
         const int item = next;
-        {  // publish the id to the other roles
+        ItemGeom g;
+        if (item >= 0) g = decode_item(item, p);
+        {  // publish the item to the other roles
           const uint32_t slot = n_pub & 1u;
           if (!mbar_wait(&item_empty[slot], ((n_pub >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-          s_item[slot] = item;
+          volatile int* w = s_geom + slot * 16;
+          if (item >= 0) {
+            w[0] = g.bh; w[1] = g.pair;
+            w[2] = g.r0[0]; w[3] = g.r0[1]; w[4] = g.r1[0]; w[5] = g.r1[1];
+            w[6] = g.lo[0]; w[7] = g.lo[1]; w[8] = g.hi[0]; w[9] = g.hi[1];
+            w[10] = g.lo_all; w[11] = g.hi_all;
+          }
+          w[12] = item;
           mbar_arrive(&item_full[slot]);
           ++n_pub;
         }
@@ -639,7 +744,9 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         // claim the following item now; the value is not needed before this item's loads are issued
         next = static_cast<int>(gridDim.x) + atomicAdd(p.sched, 1);
         if (next >= p.num_items) next = -1;
-        const ItemGeom g = decode_item(item, p);
+#ifdef FA_TRACE3
+        const uint32_t n_items = n_pub;
+#endif
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
           if (g.r1[s] < g.r0[s]) continue;
@@ -647,13 +754,14 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           ++n_q[s];
           mbar_arrive_expect_tx(&q_full[s], Cfg::kTileBytes);
           tma_load_4d(sQ + s * Cfg::kTileBytes, &mapQ, &q_full[s], 0, g.r0[s], 0, g.bh);
+          FA_TR(true, 13, 0, 4 + s);
         }
         for (int j = g.lo_all; j < g.hi_all && ok; ++j) {
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
             const uint32_t slot = it % Cfg::kStages;
             if (!mbar_wait(&kv_empty[slot], ((it / Cfg::kStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
-            FA_TR(true, 4, j - g.lo_all, t * 2 + 0);
+            FA_TR(true, 13, j - g.lo_all, t * 2 + 0);
 #ifdef FA_FAKE_LOADS  // bring-up only: after the ring has been filled once, tiles "arrive" without being loaded
             if (it >= Cfg::kStages) {
               mbar_arrive(&kv_full[slot]);
@@ -677,7 +785,11 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   tc_fence_before();
   __syncthreads();
   if (tid == 0) {
+#ifdef FA_WAIT_DEBUG
+    if (*abort_flag != 0) atomicCAS(p.status, 0, *abort_flag);
+#else
     if (*abort_flag != 0) atomicExch(p.status, 1);
+#endif
     // the last CTA to finish puts the scheduler words back to zero for the next launch
     if (atomicAdd(p.sched + 1, 1) == static_cast<int>(gridDim.x) - 1) {
       p.sched[0] = 0;
