@@ -31,6 +31,7 @@ EXPORTS = (
     "flash_forward_host_workspace_bytes",
     "flash_forward_check",
     "flash_forward_noalloc",
+    "flash_forward_noalloc_check",
     "run_flash_attention_c",
     "flash_forward_last_error",
     "flash_forward_flops",
@@ -74,6 +75,8 @@ def lib():
     L.flash_forward_host_workspace_bytes.restype = ctypes.c_size_t
     L.flash_forward_noalloc.argtypes = [vp, vp, vp, vp, i, i, i, i, f, i, i, i, vp, i, i]
     L.flash_forward_noalloc.restype = i
+    L.flash_forward_noalloc_check.argtypes = [vp, i]
+    L.flash_forward_noalloc_check.restype = i
     L.flash_forward_check.argtypes = [vp]
     L.flash_forward_check.restype = i
     L.run_flash_attention_c.argtypes = [i, i, i, i, vp, vp, vp, vp, vp, vp, i, i, i, i, i, vp, f, vp]

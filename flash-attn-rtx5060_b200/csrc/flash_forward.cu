@@ -57,7 +57,9 @@ EncodeTiledFn encode_tiled_fn() {
 constexpr int kMaxDevices = 64;
 // Each launch of the persistent kernel takes the next pair of scheduler words round-robin, so
 // that launches in flight on different streams do not share a work counter. The kernel leaves
-// its pair at zero; a pair is reused after kSchedSlots further launches on the device.
+// its pair at zero; a pair is reused after kSchedSlots further launches on the device, and a
+// launch that reuses a pair last used on ANOTHER stream first makes its stream wait for that
+// earlier launch (an event per pair), so two launches never run on one pair side by side.
 constexpr int kSchedSlots = 64;
 constexpr size_t kDeviceWords = 4 + 2 * kSchedSlots;
 struct DeviceState {
@@ -67,8 +69,34 @@ struct DeviceState {
   int num_sms = 0;
   int* status = nullptr;  // device words: [0] status, then kSchedSlots pairs of scheduler words
   unsigned next_sched = 0;
+  cudaEvent_t slot_done[kSchedSlots] = {};     // recorded behind the last launch that used the pair
+  cudaStream_t slot_stream[kSchedSlots] = {};  // the stream of that launch
+  bool slot_used[kSchedSlots] = {};
   bool attr_set[24] = {};
 };
+
+// Hands out the scheduler words for one launch on `st`. Call with s->mu held; `*slot_out` is passed to
+// sched_release() right after the launch, under the same lock.
+int sched_acquire(DeviceState* s, cudaStream_t st, int** words, int* slot_out) {
+  const int slot = (int)(s->next_sched++ % kSchedSlots);
+  cudaError_t e;
+  if (!s->slot_done[slot] &&
+      (e = cudaEventCreateWithFlags(&s->slot_done[slot], cudaEventDisableTiming)) != cudaSuccess)
+    return fail_cuda("cudaEventCreate(scheduler slot)", e);
+  if (s->slot_used[slot] && s->slot_stream[slot] != st &&
+      (e = cudaStreamWaitEvent(st, s->slot_done[slot], 0)) != cudaSuccess)
+    return fail_cuda("cudaStreamWaitEvent(scheduler slot)", e);
+  *words = s->status + 4 + 2 * slot;
+  *slot_out = slot;
+  return FA_OK;
+}
+int sched_release(DeviceState* s, cudaStream_t st, int slot) {
+  cudaError_t e = cudaEventRecord(s->slot_done[slot], st);
+  if (e != cudaSuccess) return fail_cuda("cudaEventRecord(scheduler slot)", e);
+  s->slot_stream[slot] = st;
+  s->slot_used[slot] = true;
+  return FA_OK;
+}
 DeviceState g_dev[kMaxDevices];
 
 int device_state(DeviceState** out) {
@@ -175,14 +203,13 @@ int launch_persistent_as(DeviceState* s, const CUtensorMap& mq, const CUtensorMa
   if (rc != FA_OK) return rc;
   int grid = p.num_items < s->num_sms ? p.num_items : s->num_sms;
   fa::FwdParams pp = p;
-  {
-    std::lock_guard<std::mutex> lk(s->mu);
-    pp.sched = s->status + 4 + 2 * (s->next_sched++ % kSchedSlots);
-  }
+  std::lock_guard<std::mutex> lk(s->mu);
+  int sched_slot = 0;
+  if ((rc = sched_acquire(s, st, &pp.sched, &sched_slot)) != FA_OK) return rc;
   fa::fwd_persistent_kernel<D, kAlibi, kLse><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mk, mv, pp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail_cuda("launch fwd_persistent_kernel", e);
-  return FA_OK;
+  return sched_release(s, st, sched_slot);
 }
 
 // The ALiBi bias and the log-sum-exp output are compiled in only where asked for, so the plain
@@ -207,14 +234,13 @@ int launch_runahead_as(DeviceState* s, const CUtensorMap& mq, const CUtensorMap&
   if (rc != FA_OK) return rc;
   int grid = p.num_items < s->num_sms ? p.num_items : s->num_sms;
   fa::FwdParams pp = p;
-  {
-    std::lock_guard<std::mutex> lk(s->mu);
-    pp.sched = s->status + 4 + 2 * (s->next_sched++ % kSchedSlots);
-  }
+  std::lock_guard<std::mutex> lk(s->mu);
+  int sched_slot = 0;
+  if ((rc = sched_acquire(s, st, &pp.sched, &sched_slot)) != FA_OK) return rc;
   fa::fwd_runahead_kernel<D, kAlibi, kLse><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mk, mv, pp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail_cuda("launch fwd_runahead_kernel", e);
-  return FA_OK;
+  return sched_release(s, st, sched_slot);
 }
 template <int D>
 int launch_runahead(DeviceState* s, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
@@ -229,6 +255,7 @@ int launch_runahead(DeviceState* s, const CUtensorMap& mq, const CUtensorMap& mk
 // ---- host-buffer entry point -----------------------------------------------------------
 // Per device: three streams (upload, compute, download) and the events that chain them.
 struct HostPipe {
+  std::mutex mu;  // one flash_forward_host call at a time per device: the calls share the streams and events below
   bool ready = false;
   cudaStream_t up = nullptr, run = nullptr, down = nullptr;
   cudaEvent_t in_ready[2] = {}, done[2] = {}, out_done[2] = {};
@@ -241,6 +268,7 @@ int host_pipe(HostPipe** out) {
   if (e != cudaSuccess) return fail_cuda("cudaGetDevice", e);
   if (dev < 0 || dev >= kMaxDevices) return fail(FA_UNSUPPORTED, "device ordinal out of range");
   HostPipe& hp = g_pipe[dev];
+  std::lock_guard<std::mutex> lk(hp.mu);
   if (!hp.ready) {
     if ((e = cudaStreamCreateWithFlags(&hp.up, cudaStreamNonBlocking)) != cudaSuccess ||
         (e = cudaStreamCreateWithFlags(&hp.run, cudaStreamNonBlocking)) != cudaSuccess ||
@@ -356,6 +384,11 @@ static int pick_head_group(int bh, int seqlen, int head_dim, int causal, int win
   return (bh + groups - 1) / groups;
 }
 
+// A window that reaches past either end of the sequence for every row is no window. Mapping it to
+// "unbounded" (-1) here keeps the tile arithmetic (row - window_left, row + window_right) inside int
+// for every legal argument, INT_MAX included.
+static inline int norm_window(int w, int seqlen) { return (w < 0 || w >= seqlen) ? -1 : w; }
+
 extern "C" {
 
 const char* flash_forward_last_error(void) { return g_err; }
@@ -363,6 +396,8 @@ const char* flash_forward_last_error(void) { return g_err; }
 double flash_forward_flops(int batch, int heads, int seqlen, int head_dim, int is_causal, int window_left,
                            int window_right) {
   const double bh = (double)batch * heads, n = seqlen, d = head_dim;
+  window_left = norm_window(window_left, seqlen);
+  window_right = norm_window(window_right, seqlen);
   const int wr = fa::eff_window_right(is_causal, window_right);
   if (window_left < 0 && window_right < 0) return (is_causal ? 2.0 : 4.0) * bh * n * n * d;
   double pairs = 0;  // exact count of visible (query, key) pairs of one head
@@ -380,8 +415,8 @@ int flash_forward_head_group(int batch_heads, int seqlen, int head_dim, int is_c
                              int window_right, int num_sms) {
   if (batch_heads <= 0 || seqlen <= 0 || (head_dim != 64 && head_dim != 128) || num_sms <= 0) return 0;
   const int pairs = (seqlen + 2 * fa::kBlockM - 1) / (2 * fa::kBlockM);
-  return pick_head_group(batch_heads, seqlen, head_dim, is_causal ? 1 : 0, window_left < 0 ? -1 : window_left,
-                         window_right < 0 ? -1 : window_right, pairs, num_sms);
+  return pick_head_group(batch_heads, seqlen, head_dim, is_causal ? 1 : 0, norm_window(window_left, seqlen),
+                         norm_window(window_right, seqlen), pairs, num_sms);
 }
 
 int flash_forward_kv_range(int seqlen, int is_causal, int window_left, int window_right, int row_begin,
@@ -389,8 +424,8 @@ int flash_forward_kv_range(int seqlen, int is_causal, int window_left, int windo
   if (seqlen <= 0 || row_begin < 0 || row_end < row_begin || row_end >= seqlen || !tile_begin || !tile_end ||
       !masked_tiles)
     return fail(FA_INVALID_ARG, "bad row range");
-  const int wl = window_left < 0 ? -1 : window_left;
-  const int wr = fa::eff_window_right(is_causal, window_right < 0 ? -1 : window_right);
+  const int wl = norm_window(window_left, seqlen);
+  const int wr = fa::eff_window_right(is_causal, norm_window(window_right, seqlen));
   *tile_begin = fa::kv_tile_begin(row_begin, wl);
   *tile_end = fa::kv_tile_end(row_end, wr, seqlen);
   int masked = 0;
@@ -433,8 +468,8 @@ static int forward_impl(const void* q, const void* k, const void* v, void* o, in
   p.bh = bh;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.causal = is_causal ? 1 : 0;
-  p.window_left = window_left < 0 ? -1 : window_left;
-  p.window_right = window_right < 0 ? -1 : window_right;
+  p.window_left = norm_window(window_left, seqlen);
+  p.window_right = norm_window(window_right, seqlen);
   p.status = s->status;
   p.dbg = dbg;
   p.variant = variant;
@@ -541,7 +576,9 @@ int flash_forward_check(void* stream) {
   if ((e = cudaMemcpy(&host, s->status, sizeof(int), cudaMemcpyDeviceToHost)) != cudaSuccess)
     return fail_cuda("cudaMemcpy(status)", e);
   if (host != 0) {
-    cudaMemset(s->status, 0, kDeviceWords * sizeof(int));  // a give-up may leave scheduler words non-zero
+    // Only the status word is cleared: the scheduler words belong to launches that may still be running on other
+    // streams, and a kernel that gave up still leaves its own pair at zero (every CTA reaches the final count).
+    cudaMemset(s->status, 0, sizeof(int));
     snprintf(g_err, sizeof(g_err), "a wait inside the attention kernel ran out of time (status word %d)", host);
     return FA_DEVICE_TIMEOUT;
   }
@@ -593,6 +630,7 @@ int flash_forward_host(const void* q_host, const void* k_host, const void* v_hos
   int rc = host_pipe(&hp);
   if (rc != FA_OK) return rc;
 
+  std::lock_guard<std::mutex> pipe_lock(hp->mu);
   const long long bh = (long long)batch * heads;
   const size_t head_bytes = (size_t)seqlen * head_dim * 2;
   const size_t slot_bytes = (size_t)chunk_heads * head_bytes;
@@ -600,36 +638,49 @@ int flash_forward_host(const void* q_host, const void* k_host, const void* v_hos
   auto dev_ptr = [&](int slot, int tensor) { return ws + ((size_t)slot * 4 + tensor) * slot_bytes; };
   const char* src[3] = {static_cast<const char*>(q_host), static_cast<const char*>(k_host),
                         static_cast<const char*>(v_host)};
-  cudaError_t e;
+  cudaError_t e = cudaSuccess;
+  const char* what = nullptr;  // the CUDA call that failed, if any
+#define FA_TRY(call)                                  \
+  if (!what && (e = (call)) != cudaSuccess) what = #call
   int n = 0;
-  for (long long h0 = 0; h0 < bh; h0 += chunk_heads, ++n) {
+  for (long long h0 = 0; h0 < bh && !what && rc == FA_OK; h0 += chunk_heads, ++n) {
     const int slot = n & 1;
     const int nh = (int)((bh - h0 < chunk_heads) ? (bh - h0) : chunk_heads);
     const size_t bytes = (size_t)nh * head_bytes;
     // the slot is free once the download that used it two chunks ago has finished
-    if (n >= 2 && (e = cudaStreamWaitEvent(hp->up, hp->out_done[slot], 0)) != cudaSuccess)
-      return fail_cuda("cudaStreamWaitEvent", e);
+    if (n >= 2) FA_TRY(cudaStreamWaitEvent(hp->up, hp->out_done[slot], 0));
     for (int t = 0; t < 3; ++t)
-      if ((e = cudaMemcpyAsync(dev_ptr(slot, t), src[t] + (size_t)h0 * head_bytes, bytes, cudaMemcpyHostToDevice,
-                               hp->up)) != cudaSuccess)
-        return fail_cuda("cudaMemcpyAsync(H2D)", e);
-    cudaEventRecord(hp->in_ready[slot], hp->up);
-    cudaStreamWaitEvent(hp->run, hp->in_ready[slot], 0);
-    if (n >= 2) cudaStreamWaitEvent(hp->run, hp->out_done[slot], 0);
+      FA_TRY(cudaMemcpyAsync(dev_ptr(slot, t), src[t] + (size_t)h0 * head_bytes, bytes, cudaMemcpyHostToDevice, hp->up));
+    FA_TRY(cudaEventRecord(hp->in_ready[slot], hp->up));
+    FA_TRY(cudaStreamWaitEvent(hp->run, hp->in_ready[slot], 0));
+    if (n >= 2) FA_TRY(cudaStreamWaitEvent(hp->run, hp->out_done[slot], 0));
+    if (what) break;
     rc = flash_forward(dev_ptr(slot, 0), dev_ptr(slot, 1), dev_ptr(slot, 2), dev_ptr(slot, 3), 1, nh, seqlen, head_dim,
                        softmax_scale, is_causal, window_left, window_right, hp->run);
     if (rc != FA_OK) break;
-    cudaEventRecord(hp->done[slot], hp->run);
-    cudaStreamWaitEvent(hp->down, hp->done[slot], 0);
-    if ((e = cudaMemcpyAsync(static_cast<char*>(o_host) + (size_t)h0 * head_bytes, dev_ptr(slot, 3), bytes,
-                             cudaMemcpyDeviceToHost, hp->down)) != cudaSuccess)
-      return fail_cuda("cudaMemcpyAsync(D2H)", e);
-    cudaEventRecord(hp->out_done[slot], hp->down);
+    FA_TRY(cudaEventRecord(hp->done[slot], hp->run));
+    FA_TRY(cudaStreamWaitEvent(hp->down, hp->done[slot], 0));
+    FA_TRY(cudaMemcpyAsync(static_cast<char*>(o_host) + (size_t)h0 * head_bytes, dev_ptr(slot, 3), bytes,
+                           cudaMemcpyDeviceToHost, hp->down));
+    FA_TRY(cudaEventRecord(hp->out_done[slot], hp->down));
   }
-  cudaStreamSynchronize(hp->up);
-  int rc_run = flash_forward_check(hp->run);
-  if ((e = cudaStreamSynchronize(hp->down)) != cudaSuccess && rc == FA_OK) rc = fail_cuda("cudaStreamSynchronize", e);
-  return rc != FA_OK ? rc : rc_run;
+#undef FA_TRY
+  // Whatever happened, nothing of this call may still be in flight when it returns: the copies read and write the
+  // caller's host buffers and workspace.
+  char saved[sizeof(g_err)];
+  memcpy(saved, g_err, sizeof(saved));  // the message of a failed flash_forward() above
+  const cudaError_t e_up = cudaStreamSynchronize(hp->up);
+  const int rc_run = flash_forward_check(hp->run);
+  const cudaError_t e_down = cudaStreamSynchronize(hp->down);
+  if (rc != FA_OK) {
+    memcpy(g_err, saved, sizeof(saved));
+    return rc;
+  }
+  if (what) return fail_cuda(what, e);
+  if (e_up != cudaSuccess) return fail_cuda("cudaStreamSynchronize(upload stream)", e_up);
+  if (rc_run != FA_OK) return rc_run;
+  if (e_down != cudaSuccess) return fail_cuda("cudaStreamSynchronize(download stream)", e_down);
+  return FA_OK;
 }
 
 int flash_forward_noalloc(const void* q, const void* k, const void* v, void* o, int batch, int heads, int seqlen,
@@ -672,8 +723,8 @@ int flash_forward_noalloc(const void* q, const void* k, const void* v, void* o, 
   p.bh = bh;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.causal = is_causal ? 1 : 0;
-  p.window_left = window_left < 0 ? -1 : window_left;
-  p.window_right = window_right < 0 ? -1 : window_right;
+  p.window_left = norm_window(window_left, seqlen);
+  p.window_right = norm_window(window_right, seqlen);
   p.status = words;
   p.sched = words + 2;
   p.num_q_pairs = pairs;
@@ -704,6 +755,23 @@ int flash_forward_noalloc(const void* q, const void* k, const void* v, void* o, 
   return FA_OK;
 }
 
+int flash_forward_noalloc_check(void* stream, int slot) {
+  if (slot < 0 || slot >= kNoAllocSlots) return fail(FA_INVALID_ARG, "scratch slot out of range");
+  NoAllocState* s = nullptr;
+  int rc = noalloc_state(&s);
+  if (rc != FA_OK) return rc;
+  cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail_cuda("cudaStreamSynchronize", e);
+  int host = 0;
+  if ((e = cudaMemcpy(&host, s->scratch + slot * 4, sizeof(int), cudaMemcpyDeviceToHost)) != cudaSuccess)
+    return fail_cuda("cudaMemcpy(status)", e);
+  if (host != 0) {
+    snprintf(g_err, sizeof(g_err), "a wait inside the attention kernel ran out of time (status word %d)", host);
+    return FA_DEVICE_TIMEOUT;
+  }
+  return FA_OK;
+}
+
 int flash_forward_shutdown(void) {
   int prev = 0;
   if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
@@ -717,7 +785,25 @@ int flash_forward_shutdown(void) {
     }
     s.probed = false;
     for (bool& b : s.attr_set) b = false;
+    for (int i = 0; i < kSchedSlots; ++i) {
+      if (s.slot_done[i]) {
+        cudaSetDevice(d);
+        cudaEventDestroy(s.slot_done[i]);
+        s.slot_done[i] = nullptr;
+      }
+      s.slot_used[i] = false;
+      s.slot_stream[i] = nullptr;
+    }
+    s.next_sched = 0;
+    {  // a device reset after this call invalidates the scratch address and the kernel attributes: look them up again
+      NoAllocState& na = g_noalloc[d];
+      std::lock_guard<std::mutex> lk2(na.mu);
+      na.ready = false;
+      na.scratch = nullptr;
+      na.attr_set[0] = na.attr_set[1] = false;
+    }
     HostPipe& hp = g_pipe[d];
+    std::lock_guard<std::mutex> lkp(hp.mu);
     if (hp.ready) {
       cudaSetDevice(d);
       cudaStreamDestroy(hp.up);
@@ -728,7 +814,9 @@ int flash_forward_shutdown(void) {
         cudaEventDestroy(hp.done[i]);
         cudaEventDestroy(hp.out_done[i]);
       }
-      hp = HostPipe();
+      hp.up = hp.run = hp.down = nullptr;
+      for (int i = 0; i < 2; ++i) hp.in_ready[i] = hp.done[i] = hp.out_done[i] = nullptr;
+      hp.ready = false;
     }
   }
   if (prev >= 0) cudaSetDevice(prev);

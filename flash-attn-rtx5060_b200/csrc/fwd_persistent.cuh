@@ -767,6 +767,12 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
               mbar_arrive(&kv_full[slot]);
             } else
 #endif
+#ifdef FA_TEST_WITHHOLD_LOAD  // test build only: CTA 0 never loads its fourth tile, so that a bounded wait runs out
+            if (blockIdx.x == 0 && (p.variant & 2) != 0 && it == 3) {
+              ++it;
+              continue;
+            }
+#endif
             {
               mbar_arrive_expect_tx(&kv_full[slot], Cfg::kTileBytes);
               tma_load_4d(sKV + slot * Cfg::kTileBytes, t == 0 ? &mapK : &mapV, &kv_full[slot], 0, j * kBlockN, 0, g.bh);

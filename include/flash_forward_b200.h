@@ -36,12 +36,20 @@ enum {
  *   is_causal != 0      -> key j visible to query i only if j <= i
  *   window_left  >= 0   -> key j visible only if j >= i - window_left   (< 0: unbounded)
  *   window_right >= 0   -> key j visible only if j <= i + window_right  (< 0: unbounded)
+ *                          (any value up to INT_MAX is legal; a window of seqlen or more is unbounded)
  *   stream              -> a cudaStream_t passed as void* (NULL = default stream)
  *
  * head_dim must be 64 or 128 (reference: src/flash_forward.h:588). seqlen may be any positive
  * value (the reference silently requires a multiple of 128). Pointers must be 16-byte aligned.
  * The call returns once the kernel is enqueued; use flash_forward_check() to learn whether a
  * device-side wait timed out.
+ *
+ * Launches in flight: every launch takes one of 64 pairs of scheduler words (device scratch of a
+ * few hundred bytes, allocated on the first call per device) in turn. Launches on one stream are
+ * ordered anyway; when a pair is reused by a launch on ANOTHER stream, that stream is first made to
+ * wait (cudaStreamWaitEvent) for the earlier launch, so any number of launches may be queued on any
+ * number of streams. Because of that event the call must not be made while its stream is being
+ * captured into a CUDA graph: a captured launch would keep its pair for every replay.
  */
 int flash_forward(const void* q, const void* k, const void* v, void* o, int batch, int heads, int seqlen,
                   int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,
@@ -108,7 +116,10 @@ size_t flash_forward_host_workspace_bytes(int seqlen, int head_dim, int chunk_he
 
 /* Waits for `stream`, then reads and clears the current device's status word. Returns FA_OK,
  * FA_DEVICE_TIMEOUT, or FA_CUDA_ERROR. Replaces the reference's CUDA_CHECK(cudaDeviceSynchronize())
- * + exit (src/flash_forward.h:654-655). */
+ * + exit (src/flash_forward.h:654-655). There is ONE status word per device, not per stream: a
+ * time-out raised by a launch on another stream of the device is reported (and consumed) by whichever
+ * check comes first. Like flash_forward() it allocates the device's scratch on first use; hosts that
+ * must not allocate use flash_forward_noalloc() and flash_forward_noalloc_check(). */
 int flash_forward_check(void* stream);
 
 /* The reference's host entry point, positional argument for positional argument
@@ -161,9 +172,10 @@ int flash_forward_kv_range(int seqlen, int is_causal, int window_left, int windo
  *   slot  which of the 16 four-word scratch slots this call uses, 0..15. Anything else is
  *         rejected with FA_INVALID_ARG; so is a problem whose work-item count
  *         batch*heads*ceil(seqlen/256) does not fit the slot's 32-bit work counter.
- *   wait  0: return once the work is enqueued on `stream` (a device-side time-out then goes
- *         unreported); non-zero: block until the kernel has finished and return
- *         FA_DEVICE_TIMEOUT if its status word was set.
+ *   wait  0: return once the work is enqueued on `stream` (flash_forward_noalloc_check() reads the
+ *         slot's status later; flash_forward_check() is NOT for these hosts, it allocates);
+ *         non-zero: block until the kernel has finished and return FA_DEVICE_TIMEOUT if its status
+ *         word was set.
  *
  * All other arguments as for flash_forward(). A slot keeps the contents the last call left in it;
  * every call first clears its slot on `stream`. Calls that use the same slot must not overlap on
@@ -175,7 +187,15 @@ int flash_forward_noalloc(const void* q, const void* k, const void* v, void* o, 
                           int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,
                           void* stream, int slot, int wait);
 
-/* Frees the per-device status words this library allocated. Optional. */
+/* Status of the last flash_forward_noalloc() call on scratch slot `slot` of the current device: waits
+ * for `stream`, reads the slot's status word (a 4-byte device-to-host copy; nothing is allocated) and
+ * returns FA_OK or FA_DEVICE_TIMEOUT. The word is cleared by the next call on that slot. No counterpart
+ * in the reference. */
+int flash_forward_noalloc_check(void* stream, int slot);
+
+/* Frees the per-device status words, events and streams this library created, and forgets what it
+ * learned about each device (scratch addresses, kernel attributes), so that it can be used again
+ * after a device reset. Optional. */
 int flash_forward_shutdown(void);
 
 #ifdef __cplusplus

@@ -118,6 +118,22 @@ def test_tile_plan_matches_brute_force(pkg, N, causal, wl, wr):
         assert masked == want_masked, (r0, masked, want_masked)
 
 
+def test_windows_up_to_int_max(pkg):
+    """Window arguments are legal up to INT_MAX: the host-side plan and the FLOP count treat a window that covers
+    the sequence as no window instead of overflowing `row + window`."""
+    big = 2 ** 31 - 1
+    for N in (127, 1000, 2048):
+        for causal in (False, True):
+            assert pkg.flops(2, 3, N, 64, causal, big, big) == pkg.flops(2, 3, N, 64, causal, -1, -1)
+            assert pkg.flops(2, 3, N, 64, causal, N, N + 5) == pkg.flops(2, 3, N, 64, causal, -1, -1)
+            assert pkg.flops(2, 3, N, 64, causal, 10, big) == pkg.flops(2, 3, N, 64, causal, 10, -1)
+            for r0 in range(0, N, 128):
+                r1 = min(r0 + 128, N) - 1
+                assert pkg.kv_range(N, causal, big, big, r0, r1) == pkg.kv_range(N, causal, -1, -1, r0, r1)
+                assert pkg.kv_range(N, causal, 100, big, r0, r1) == pkg.kv_range(N, causal, 100, -1, r0, r1)
+            assert pkg.head_group(64, N, 64, causal, big, big) == pkg.head_group(64, N, 64, causal, -1, -1)
+
+
 def test_head_group_policy(pkg):
     # no mask: head-major order
     assert pkg.head_group(64, 8192, 128) == 1

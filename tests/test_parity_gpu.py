@@ -31,6 +31,61 @@ def assert_close(ob, got, want, max_abs=MAX_ABS, mean_abs=MEAN_ABS):
     return mx, mean
 
 
+def fp16_ulp(x):
+    """Spacing of fp16 numbers at |x| (subnormal spacing below 2^-14)."""
+    a = np.abs(x.astype(np.float32))
+    e = np.floor(np.log2(np.maximum(a, 2.0 ** -14)))
+    return np.exp2(e - 10).astype(np.float32)
+
+
+def exact_rows(q, k, v, b, h, rows, scale, causal, wl, wr):
+    """fp64 attention of the given rows of one head (numpy): the error-free answer for those rows."""
+    q64, k64, v64 = (a[b, h].astype(np.float64) for a in (q, k, v))
+    n = k64.shape[0]
+    out = np.empty((len(rows), v64.shape[1]))
+    j = np.arange(n)
+    for t, i in enumerate(rows):
+        vis = np.ones(n, bool)
+        if causal:
+            vis &= j <= i
+        if wl >= 0:
+            vis &= j >= i - wl
+        if wr >= 0 and not causal:
+            vis &= j <= i + wr
+        s = (k64[vis] @ q64[i]) * scale
+        p = np.exp(s - s.max())
+        out[t] = (p / p.sum()) @ v64[vis]
+    return out
+
+
+def assert_close_or_one_ulp(got, want, mean_abs=MEAN_ABS, exact=None):
+    """The acceptance bar where 2e-3 is no longer more than the oracle's own rounding: every element is within
+    2e-3 of the oracle, OR within one fp16 ulp of the oracle's value (3.9e-3 at |o| >= 4), OR - where `exact` is given
+    - the element is one of the few on which the oracle itself is the noisy side: it rounds every p*v product to
+    fp16, so a row whose terms reach 2..4 and cancel carries up to 2e-3 of noise at any |o|; such an element passes
+    only if the kernel is within 1e-3 of the fp64 answer. `exact(b, h, rows)` returns fp64 rows. The mean bar is
+    unchanged. Prints the worst distance in ulps beside the absolute one."""
+    g32, w32 = got.astype(np.float32), want.astype(np.float32)
+    assert np.isfinite(g32).all()
+    diff = np.abs(g32 - w32)
+    ulps = diff / fp16_ulp(want)
+    worst = int(np.argmax(diff))
+    print(f"max_abs={diff.max():.3e} at |o|={abs(w32.flat[worst]):.3f} ({ulps.flat[worst]:.2f} ulp of the oracle value); "
+          f"mean_abs={diff.mean():.3e}")
+    bad = np.argwhere((diff > MAX_ABS) & (ulps > 1.0))
+    if len(bad) and exact is not None:
+        assert len(bad) <= 16, f"{len(bad)} elements beyond both 2e-3 and one fp16 ulp"
+        for b, h, i, c in bad:
+            ex = exact(b, h, [i])[0, c]
+            err_kernel, err_oracle = abs(g32[b, h, i, c] - ex), abs(w32[b, h, i, c] - ex)
+            print(f"  element {(b, h, i, c)}: kernel {g32[b, h, i, c]:.5f} oracle {w32[b, h, i, c]:.5f} fp64 {ex:.5f}")
+            assert err_kernel <= 1e-3 and err_kernel <= err_oracle, (err_kernel, err_oracle)
+    else:
+        assert len(bad) == 0, (f"{len(bad)} elements beyond both 2e-3 and one fp16 ulp; worst {diff.max():.3e} "
+                               f"at |o|={abs(w32.flat[worst]):.3f}")
+    assert diff.mean() <= mean_abs, f"mean_abs={diff.mean():.3e}"
+
+
 def test_golden_alibi(pkg, ob):
     """The reference's ALiBi bias (src/mask.h:21-26, src/main.cu:200-207) against the golden vector made by its CPU
     function, through both the native entry point and the reference's positional one."""
@@ -64,7 +119,7 @@ def test_alibi_against_oracle(pkg, ob, N, d, causal, w):
     out = pkg.attention_forward(tq, tk, tv, causal=causal, window_left=w, window_right=w,
                                 alibi_slopes=torch.from_numpy(slopes).cuda())
     pkg.check(torch.cuda.current_stream().cuda_stream)
-    assert_close(ob, out.cpu().numpy(), want, max_abs=4e-3)  # the positive bias concentrates mass: |o| passes 4
+    assert_close_or_one_ulp(out.cpu().numpy(), want)  # the positive bias concentrates mass: |o| passes 4
 
 
 @pytest.mark.parametrize("kernel", [0, 1])
@@ -162,9 +217,9 @@ def test_very_long_sequence_and_very_many_heads(pkg, ob):
     q, k, v = make_inputs(6000, 6000, 1, 256, 64)
     got = run_gpu(pkg, q, k, v, True, 100, -1)
     want = ob.attention(q, k, v, causal=True, window_left=100, window_right=-1)
-    # 98 M outputs, the early causal rows are averages of a handful of N(0,1) values: some exceed 2, where one
-    # fp16 ulp is already 1.95e-3 (two ulps were seen once in 98 M), so the bound on the maximum is two ulps there
-    assert_close(ob, got, want, max_abs=4e-3)
+    # 98 M outputs; the early causal rows are averages of a handful of N(0,1) values and some exceed 4, where one
+    # fp16 ulp is 3.9e-3
+    assert_close_or_one_ulp(got, want, exact=lambda b, h, rows: exact_rows(q, k, v, b, h, rows, 0.125, True, 100, -1))
 
 
 @pytest.mark.parametrize("kernel", [0, 1])
@@ -222,6 +277,44 @@ def test_cta_pair_kernel_many_items(pkg, ob, B, H, N, causal, wl):
     assert_close(ob, got[:1, heads].cpu().numpy(), want)
 
 
+def test_windows_up_to_int_max_are_unbounded(pkg, ob):
+    """Any window value is legal; one that covers the whole sequence must give the unwindowed result bit for bit
+    (the tile arithmetic works on `row - window_left` and `row + window_right`, so INT_MAX must not reach it)."""
+    big = 2 ** 31 - 1
+    q, k, v = make_inputs(91, 1, 2, 777, 64)   # ragged length: the tail tile is masked
+    plain = run_gpu(pkg, q, k, v, False, -1, -1)
+    assert np.array_equal(plain.view(np.uint16), run_gpu(pkg, q, k, v, False, big, big).view(np.uint16))
+    assert np.array_equal(plain.view(np.uint16), run_gpu(pkg, q, k, v, False, big, -1).view(np.uint16))
+    assert np.array_equal(plain.view(np.uint16), run_gpu(pkg, q, k, v, False, 777, 100000).view(np.uint16))
+    causal = run_gpu(pkg, q, k, v, True, -1, -1)
+    assert np.array_equal(causal.view(np.uint16), run_gpu(pkg, q, k, v, True, big, big).view(np.uint16))
+    one_sided = run_gpu(pkg, q, k, v, False, 50, big)
+    assert_close(ob, one_sided, ob.attention(q, k, v, window_left=50, window_right=-1))
+
+
+def test_many_launches_on_two_streams(pkg):
+    """More launches than the library has scheduler slots (64), alternating between two streams with nothing
+    synchronising them: a launch that reuses a slot last used on the other stream must wait for that launch, or the
+    two would share a work counter and rows would be left unwritten."""
+    import torch
+
+    g = torch.Generator(device="cuda").manual_seed(7)
+    B, H, N, d = 1, 24, 1024, 64
+    q, k, v = (torch.randn((B, H, N, d), generator=g, device="cuda", dtype=torch.float16) for _ in range(3))
+    want = pkg.attention_forward(q, k, v, causal=True)
+    pkg.check(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    outs = [torch.full_like(q, float("nan")) for _ in range(200)]
+    for i, o in enumerate(outs):
+        pkg.flash_forward(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), B, H, N, d, is_causal=True,
+                          stream=streams[i & 1].cuda_stream)
+    for st in streams:
+        pkg.check(st.cuda_stream)
+    for o in outs:
+        assert torch.equal(o, want)
+
+
 def exact_attention(q, k, v, scale, causal):
     """fp64 attention of fp16 inputs (numpy), rounded once to fp16: the error-free answer."""
     q64, k64, v64 = (a.astype(np.float64) for a in (q, k, v))
@@ -260,7 +353,7 @@ def test_growing_row_max_forces_rescale(pkg, ob):
     for kernel in (0, 1):
         got = run_gpu(pkg, q, k, v, False, -1, -1, kernel, scale=1.0)
         want = ob.attention(q, k, v, scale=1.0)
-        assert_close(ob, got, want, max_abs=4e-3)
+        assert_close_or_one_ulp(got, want)
 
 
 def test_deterministic_and_kernels_agree(pkg, ob):

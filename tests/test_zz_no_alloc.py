@@ -77,3 +77,82 @@ def test_noalloc_rejects_what_the_scratch_cannot_hold(pkg):
     assert b"work items" in pkg.lib().flash_forward_last_error()
     assert pkg.lib().flash_forward_noalloc(t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), 1, 1, 128, 96, 0.0,
                                            0, -1, -1, None, 0, 1) == pkg.FA_UNSUPPORTED
+
+
+_FRESH_PROCESS_SCRIPT = r"""
+import ctypes, sys
+import numpy as np
+import torch
+sys.path.insert(0, {root!r})
+import __graft_entry__ as entry
+pkg = entry.load_package()
+L = pkg.lib()
+rt = ctypes.CDLL("libcudart.so." + torch.version.cuda.split(".")[0], mode=ctypes.RTLD_GLOBAL)
+def free_bytes():
+    f, t = ctypes.c_size_t(), ctypes.c_size_t()
+    assert rt.cudaMemGetInfo(ctypes.byref(f), ctypes.byref(t)) == 0
+    return f.value
+B, H, N, d = 1, 3, 640, 128
+g = torch.Generator(device="cuda").manual_seed(5)
+q, k, v = (torch.randn((B, H, N, d), generator=g, device="cuda", dtype=torch.float16) for _ in range(3))
+outs = [torch.empty_like(q) for _ in range(4)]
+torch.cuda.synchronize()
+def call(o, slot, wait):
+    return L.flash_forward_noalloc(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), B, H, N, d, 0.0, 1, -1, -1,
+                                   None, slot, wait)
+assert call(outs[0], 2, 1) == 0          # first call on the device: one-time set-up
+before = free_bytes()
+assert call(outs[1], 2, 1) == 0
+assert call(outs[2], 7, 0) == 0
+assert L.flash_forward_noalloc_check(None, 7) == 0
+assert call(outs[3], 2, 1) == 0
+after = free_bytes()
+assert before == after, (before, after)  # nothing was allocated on the device by any of the calls
+for o in outs[1:]:
+    assert torch.equal(o, outs[0])
+# the ordinary entry point was never used in this process, so its scratch was never allocated either
+ref = torch.softmax((q.float() @ k.float().transpose(-1, -2) / d ** 0.5).masked_fill(
+    torch.triu(torch.ones(N, N, dtype=torch.bool, device="cuda"), 1), float("-inf")), -1) @ v.float()
+assert (outs[0].float() - ref).abs().max().item() <= 4e-3
+print("NOALLOC-OK")
+"""
+
+
+def test_noalloc_allocates_nothing_in_a_fresh_process(pkg):
+    """The defining property, checked where nothing else can hide it: a new process that only ever calls
+    flash_forward_noalloc (so the ordinary entry point's cudaMalloc never runs) sees the same free device memory
+    before and after further calls, and the allocation-free status read works."""
+    import subprocess
+    import sys
+
+    from conftest import ROOT
+
+    r = subprocess.run([sys.executable, "-c", _FRESH_PROCESS_SCRIPT.format(root=ROOT)], capture_output=True, text=True,
+                       timeout=300)
+    assert r.returncode == 0 and "NOALLOC-OK" in r.stdout, r.stdout + r.stderr
+
+
+def test_noalloc_on_a_second_device_and_after_shutdown(pkg):
+    """The scratch address belongs to a device: a call on device 1 must look it up there, and a call after
+    flash_forward_shutdown() must look it up again."""
+    import torch
+
+    B, H, N, d = 1, 2, 384, 64
+    devices = [0] + ([1] if torch.cuda.device_count() > 1 else [])
+    results = []
+    for rep in range(2):
+        for dev in devices:
+            with torch.cuda.device(dev):
+                g = torch.Generator(device=f"cuda:{dev}").manual_seed(9)
+                q, k, v = (torch.randn((B, H, N, d), generator=g, device=f"cuda:{dev}", dtype=torch.float16)
+                           for _ in range(3))
+                o = torch.full_like(q, float("nan"))
+                assert call_noalloc(pkg, q, k, v, o, B, H, N, d, True, -1, -1, slot=1) == pkg.FA_OK
+                ref = pkg.attention_forward(q, k, v, causal=True)
+                torch.cuda.synchronize()
+                assert torch.equal(o, ref)
+                results.append(o.cpu())
+        torch.cuda.synchronize()
+        assert pkg.lib().flash_forward_shutdown() == pkg.FA_OK
+    for r in results[1:]:
+        assert torch.equal(r, results[0])
