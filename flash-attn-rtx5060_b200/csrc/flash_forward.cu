@@ -19,7 +19,6 @@
 #include "fwd_params.h"
 #include "fwd_pair_ahead.cuh"
 #include "fwd_persistent.cuh"
-#include "fwd_runahead.cuh"
 #include "fwd_serial.cuh"
 
 namespace {
@@ -72,7 +71,7 @@ struct DeviceState {
   cudaEvent_t slot_done[kSchedSlots] = {};     // recorded behind the last launch that used the pair
   cudaStream_t slot_stream[kSchedSlots] = {};  // the stream of that launch
   bool slot_used[kSchedSlots] = {};
-  bool attr_set[24] = {};
+  bool attr_set[12] = {};
 };
 
 // Hands out the scheduler words for one launch on `st`. Call with s->mu held; `*slot_out` is passed to
@@ -222,34 +221,6 @@ int launch_persistent(DeviceState* s, const CUtensorMap& mq, const CUtensorMap& 
                         : launch_persistent_as<D, true, false>(s, mq, mk, mv, p, st);
   return lse ? launch_persistent_as<D, false, true>(s, mq, mk, mv, p, st)
              : launch_persistent_as<D, false, false>(s, mq, mk, mv, p, st);
-}
-
-// Kernel whose score products run ahead of the softmax (64-key tiles, two score buffers per q tile).
-template <int D, bool kAlibi, bool kLse>
-int launch_runahead_as(DeviceState* s, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                       const fa::FwdParams& p, cudaStream_t st) {
-  using Cfg = fa::RunaheadCfg<D>;
-  constexpr int slot = 12 + (kLse ? 4 : 0) + (kAlibi ? 2 : 0) + (D == 64 ? 0 : 1);
-  int rc = ensure_smem_attr(s, slot, fa::fwd_runahead_kernel<D, kAlibi, kLse>, Cfg::kSmemBytes);
-  if (rc != FA_OK) return rc;
-  int grid = p.num_items < s->num_sms ? p.num_items : s->num_sms;
-  fa::FwdParams pp = p;
-  std::lock_guard<std::mutex> lk(s->mu);
-  int sched_slot = 0;
-  if ((rc = sched_acquire(s, st, &pp.sched, &sched_slot)) != FA_OK) return rc;
-  fa::fwd_runahead_kernel<D, kAlibi, kLse><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mk, mv, pp);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return fail_cuda("launch fwd_runahead_kernel", e);
-  return sched_release(s, st, sched_slot);
-}
-template <int D>
-int launch_runahead(DeviceState* s, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                    const fa::FwdParams& p, cudaStream_t st) {
-  const bool alibi = p.alibi_slopes != nullptr, lse = p.lse != nullptr;
-  if (alibi) return lse ? launch_runahead_as<D, true, true>(s, mq, mk, mv, p, st)
-                        : launch_runahead_as<D, true, false>(s, mq, mk, mv, p, st);
-  return lse ? launch_runahead_as<D, false, true>(s, mq, mk, mv, p, st)
-             : launch_runahead_as<D, false, false>(s, mq, mk, mv, p, st);
 }
 
 // ---- host-buffer entry point -----------------------------------------------------------
@@ -441,7 +412,7 @@ static int forward_impl(const void* q, const void* k, const void* v, void* o, in
                         float* lse = nullptr) {
   if (!q || !k || !v || !o) return fail(FA_INVALID_ARG, "null tensor pointer");
   if (reinterpret_cast<uintptr_t>(lse) & 3) return fail(FA_INVALID_ARG, "lse must be 4-byte aligned");
-  if (lse && kernel != 0 && kernel != 3) return fail(FA_UNSUPPORTED, "only kernels 0 and 3 write the log-sum-exp");
+  if (lse && kernel != 0) return fail(FA_UNSUPPORTED, "only the default kernel writes the log-sum-exp");
   if (alibi_slopes && kernel == 1) return fail(FA_UNSUPPORTED, "the serial kernel has no ALiBi path");
   if (batch <= 0 || heads <= 0 || seqlen <= 0) return fail(FA_INVALID_ARG, "batch, heads and seqlen must be positive");
   if (head_dim != 64 && head_dim != 128) return fail(FA_UNSUPPORTED, "head_dim must be 64 or 128");
@@ -449,7 +420,7 @@ static int forward_impl(const void* q, const void* k, const void* v, void* o, in
        reinterpret_cast<uintptr_t>(o)) & 15)
     return fail(FA_INVALID_ARG, "tensor pointers must be 16-byte aligned");
   if ((long long)batch * heads > 0x7fffffffLL) return fail(FA_INVALID_ARG, "batch*heads overflows int");
-  if (kernel < 0 || kernel > 3) return fail(FA_INVALID_ARG, "kernel must be 0 (default), 1 (serial), 2 (CTA pair) or 3 (run-ahead)");
+  if (kernel < 0 || kernel > 2) return fail(FA_INVALID_ARG, "kernel must be 0 (default), 1 (serial) or 2 (CTA pair)");
   if (kernel == 2 && head_dim != 128) return fail(FA_UNSUPPORTED, "the CTA-pair kernel needs head_dim 128");
   if (!(softmax_scale == softmax_scale)) return fail(FA_INVALID_ARG, "softmax_scale is NaN");
 
@@ -480,10 +451,6 @@ static int forward_impl(const void* q, const void* k, const void* v, void* o, in
   if ((long long)bh * p.num_q_pairs > 0x7fffffffLL) return fail(FA_INVALID_ARG, "too many work items");
   p.num_items = bh * p.num_q_pairs;
   p.head_group = pick_head_group(bh, seqlen, head_dim, p.causal, p.window_left, p.window_right, p.num_q_pairs, s->num_sms);
-  if (const char* e = getenv("FA_HEAD_GROUP")) {  // tuning knob for experiments
-    const int v = atoi(e);
-    if (v > 0) p.head_group = v < bh ? v : bh;
-  }
 
   CUtensorMap mq, mk, mv;
   if ((rc = make_map(&mq, q, bh, seqlen, head_dim, fa::kBlockM)) != FA_OK) return rc;
@@ -491,15 +458,6 @@ static int forward_impl(const void* q, const void* k, const void* v, void* o, in
   if ((rc = make_map(&mv, v, bh, seqlen, head_dim, fa::kBlockN)) != FA_OK) return rc;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (const char* e = getenv("FA_KERNEL")) {  // experiment switch
-    if (kernel == 0 && atoi(e) == 3) kernel = 3;
-  }
-  if (kernel == 3) {
-    CUtensorMap mk64, mv64;
-    if ((rc = make_map(&mk64, k, bh, seqlen, head_dim, 64)) != FA_OK) return rc;
-    if ((rc = make_map(&mv64, v, bh, seqlen, head_dim, 64)) != FA_OK) return rc;
-    return head_dim == 64 ? launch_runahead<64>(s, mq, mk64, mv64, p, st) : launch_runahead<128>(s, mq, mk64, mv64, p, st);
-  }
   if (kernel == 2) return launch_pair_ahead(s, q, k, v, p, st);
   if (kernel == 1) {
     return head_dim == 64 ? launch_serial<64>(s, mq, mk, mv, p, st) : launch_serial<128>(s, mq, mk, mv, p, st);

@@ -29,19 +29,6 @@
 
 namespace fa {
 
-// Bring-up only: with FA_AHEAD_PROF one thread per role of cluster 0's even CTA adds the clocks it spends in each
-// phase into p.dbg (64-bit counters, 16 per role).
-#ifdef FA_AHEAD_PROF
-#define FA_AP_DECL long long ap_t = clock64(); long long ap_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
-#define FA_AP(i) { const long long ap_n = clock64(); ap_acc[i] += ap_n - ap_t; ap_t = ap_n; }
-#define FA_AP_STORE(cond, role) if ((cond) && p.dbg != nullptr) { for (int ap_i = 0; ap_i < 8; ++ap_i) \
-    reinterpret_cast<long long*>(p.dbg)[(role) * 16 + ap_i] = ap_acc[ap_i]; }
-#else
-#define FA_AP_DECL
-#define FA_AP(i)
-#define FA_AP_STORE(cond, role)
-#endif
-
 struct AheadCfg {
   static constexpr int D = 128;
   static constexpr int kThreads = 512;
@@ -251,7 +238,6 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     const uint64_t scale2 = f2_pack(sl2, sl2);
     uint32_t t = 0, n_item = 0;
     bool ok = true;
-    FA_AP_DECL;
     for (int round = 0; ok; ++round) {
       const int item = pair_item(round, cluster_id, num_clusters, p.num_items);
       if (item == -2) break;
@@ -266,10 +252,8 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       for (int j = g.lo; j < g.hi; ++j, ++t) {
         if ((t & 1u) != w) continue;
         const uint32_t ph = (t >> 1) & 1u;
-        FA_AP(0);
         if (!mbar_wait_warp(&s_full[w], ph, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        FA_AP(1);
 #ifdef FA_AHEAD_FAKE  // bring-up only: the load + tensor pipeline of the pair without the softmax work
         tc_fence_before();
         __syncwarp();
@@ -307,7 +291,6 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive_peer(s_free_even[w]);
-          FA_AP(2);
           float sc[kBlockN];
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -339,7 +322,6 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             mx3 = max3(mx3, sc[c + 6], sc[c + 7]);
           }
           const float m_tile = max3(mx0, mx1, fmaxf(mx2, mx3));
-          FA_AP(3);
           // Reference max after the previous tile, from the group that owns it. Every publication is waited
           // for, also across item boundaries (where its value is not used), so the two groups take strict
           // turns on these barriers. NaN marks "no finite score seen in this row so far".
@@ -367,12 +349,10 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           sAlpha[(t & 3u) * kBlockM + row_l] = alpha;
           __syncwarp();
           if (lane == 0) mbar_arrive(&alpha_ready[t & 3u]);
-          FA_AP(4);
           // The two warps that share an SM sub-partition (same rows, one per group) take turns on its MUFU:
           // without this the groups settle into running their exponentials at the same time at half rate
           // each, and their loads, maxima and waits at the same time too, so nothing overlaps.
           if (t > 0 && !mbar_wait_warp(e_other, ((t - 1u) >> 1) & 1u, abort_flag)) return false;
-          FA_AP(7);
           // P(t - 2) V(t - 2) has completed: its P buffer may be overwritten.
           if (!mbar_wait_warp(&p_free[w], ph ^ 1u, abort_flag)) return false;
           const float neg_ms = -m_use * sl2;
@@ -380,21 +360,19 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           uint64_t lsum_a = 0ull, lsum_b = 0ull;
           uint32_t pk0[32], pk1[32];
           // masked tiles hold -inf scores, which only the MUFU path maps to 0
-          exp_half_tile<!kMasked>(sc, scale2, negms2, pk0, lsum_a, lsum_b);
+          exp_half_tile(sc, scale2, negms2, pk0, lsum_a, lsum_b);
           tmem_st32(tP + 0, pk0);
-          exp_half_tile<!kMasked>(sc + 64, scale2, negms2, pk1, lsum_a, lsum_b);
+          exp_half_tile(sc + 64, scale2, negms2, pk1, lsum_a, lsum_b);
           __syncwarp();
           if (lane == 0) mbar_arrive(e_mine);
           float l0, l1;
           f2_unpack(f2_add(lsum_a, lsum_b), l0, l1);
           l_part = l_part * shift + (l0 + l1);
-          FA_AP(5);
           tmem_st32(tP + 32, pk1);
           tmem_wait_st();
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive_peer(p_full_even[w]);  // the whole P tile is in TMEM
-          FA_AP(6);
           return true;
         };
         if (kv_tile_needs_mask(kv0, g.r0, g.r1, wl, wr, N)) ok = tile_body(std::true_type{});
@@ -409,7 +387,6 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       if (lane == 0) mbar_arrive(&l_ready[w]);
       ++n_item;
     }
-    FA_AP_STORE(blockIdx.x == 0 && tid == 0, 0);
   } else if (warp < 12) {
     // =====================================================================================
     // correction + epilogue for this CTA's rows
@@ -505,14 +482,11 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       const uint32_t q_addr = smem_u32(sQ);
       const uint32_t kv_addr = smem_u32(sKV);
       bool ok = true;
-      FA_AP_DECL;
 
       auto wait_slot = [&](uint32_t it) -> bool {  // both halves of ring entry `it` have landed
         const uint32_t slot = it % Cfg::kStages, par = (it / Cfg::kStages) & 1u;
         if (!mbar_wait_warp(&kv_full[slot], par, abort_flag)) return false;
-        FA_AP(it & 1u ? 4 : 1);
         const bool landed = mbar_wait_warp(&kv_peer[slot], par, abort_flag);
-        FA_AP(7);
         return landed;
       };
       auto issue_scores = [&](const AheadCursor& c) -> bool {  // S(t) = Q K(t)^T for both CTAs
@@ -522,11 +496,9 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           if (!mbar_wait_warp(&q_full[qb], qph, abort_flag)) return false;
           if (!mbar_wait_warp(&q_peer[qb], qph, abort_flag)) return false;
         }
-        FA_AP(0);
         if (!wait_slot(2u * c.t)) return false;
         if (!mbar_wait_warp(&s_free[b], ph ^ 1u, abort_flag)) return false;  // S(t - 2) has been read
         tc_fence_after();
-        FA_AP(2);
         const uint32_t slot = (2u * c.t) % Cfg::kStages;
         const uint64_t kdesc = kdesc0 + ((kv_addr + slot * Cfg::kSlotBytes) >> 4);
         const uint64_t qdesc = kdesc0 + ((q_addr + qb * Cfg::kQTileBytes) >> 4);
@@ -542,7 +514,6 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           if (c.j + 1 == c.g.hi) umma_commit_2cta(&q_empty[qb], 3);
         }
         __syncwarp();
-        FA_AP(3);
         return true;
       };
       auto issue_pv = [&](const AheadCursor& c) -> bool {  // O += P(t) V(t) for both CTAs
@@ -553,7 +524,6 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         }
         if (!mbar_wait_warp(&p_full[b], ph, abort_flag)) return false;
         tc_fence_after();
-        FA_AP(5);
         const uint32_t slot = (2u * c.t + 1u) % Cfg::kStages;
         const uint64_t vdesc = vdesc0 + ((kv_addr + slot * Cfg::kSlotBytes) >> 4);
         const uint32_t tP = tmem_base + Cfg::kColP + 64u * b;
@@ -567,7 +537,6 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           if (c.j + 1 == c.g.hi) umma_commit_2cta(o_full, 3);
         }
         __syncwarp();
-        FA_AP(6);
         return true;
       };
 
@@ -587,7 +556,6 @@ fwd_pair_ahead_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           c.advance(p, rank, cluster_id, num_clusters);
         }
       }
-      FA_AP_STORE(blockIdx.x == 0 && lane == 0, warp == 12 ? 1 : 2);
     } else if (warp == 12 && rank == 1 && lane == 0) {
       // ===================================================================================
       // odd CTA: tell the issuer when this CTA's Q tile and K/V halves have landed

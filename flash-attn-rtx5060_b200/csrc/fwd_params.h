@@ -23,7 +23,8 @@ struct FwdParams {
   int window_right;  // j <= i + window_right  (< 0: unbounded); forced to 0 by `causal`
   int* status;       // device word, 0 = ok; set non-zero when a bounded wait gave up
   float* dbg;        // optional bring-up dump (serial kernel only), else nullptr
-  int variant;       // serial kernel only: bit0 = P through shared memory instead of TMEM
+  int variant;       // bit0 (serial kernel): P through shared memory instead of TMEM; bit1 (test build of the
+                     // persistent kernel only): CTA 0 withholds one tile so that a bounded wait runs out
   // persistent kernel only
   int num_q_pairs;   // ceil(seqlen / 256)
   int num_items;     // bh * num_q_pairs

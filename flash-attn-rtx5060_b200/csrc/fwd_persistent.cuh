@@ -33,52 +33,7 @@
 #define FA_REG_MISC 72
 #endif
 
-// Of every 8 pairs of scores, this many pairs take their 2^x from a polynomial on the FMA pipe
-// instead of the MUFU unit, whose 16 results per clock per SM would otherwise bound the kernel.
-#ifndef FA_EMU_PAIRS
-#define FA_EMU_PAIRS 0
-#endif
 
-
-// Optional timeline capture for kernel bring-up (compile with -DFA_TRACE and pass a dbg buffer):
-// CTA 0 records clock64() stamps of its first work item, 8 stamps per (role, iteration).
-#if defined(FA_TRACE3)
-// boundary trace: the last 44 rounds of CTA 0's first work item land in rows 0..43, the first 20 rounds of its
-// second item in rows 44..63
-#define FA_TR(cond, role, iter, slot)                                                                  \
-  do {                                                                                                 \
-    if (blockIdx.x == 0 && p.dbg != nullptr && (cond)) {                                               \
-      int it_ = -1;                                                                                    \
-      if (n_items == 1) { it_ = (iter) - (g.hi_all - g.lo_all - 40); if (it_ >= 44) it_ = -1; }        \
-      else if (n_items == 2 && (iter) >= 0 && (iter) < 20) it_ = 44 + (iter);                          \
-      if (it_ >= 0 && it_ < 64) reinterpret_cast<long long*>(p.dbg)[((role) * 64 + it_) * 8 + (slot)] = clock64(); \
-    }                                                                                                  \
-  } while (0)
-#elif defined(FA_TRACE)
-#define FA_TR(cond, role, iter, slot)                                                             \
-  do {                                                                                            \
-    if (blockIdx.x == 0 && item == 0 && p.dbg != nullptr && (cond) && (iter) >= 0 && (iter) < 64) \
-      reinterpret_cast<long long*>(p.dbg)[((role) * 64 + (iter)) * 8 + (slot)] = clock64();      \
-  } while (0)
-#else
-#define FA_TR(cond, role, iter, slot) \
-  do {                                \
-  } while (0)
-#endif
-
-// Stamps of the tensor issuer: timeline entries under FA_TRACE; under FA_PROF (bring-up) each stamp
-// adds the clocks since the previous one to an accumulator chosen by the call site, and CTA 0
-// writes the sums to the dbg buffer.
-#if defined(FA_PROF)
-#define FA_TM(role, iter, slot)                                        \
-  do {                                                                 \
-    const uint32_t t_now = static_cast<uint32_t>(clock());             \
-    prof_acc[((role) == 14 ? 8 : 0) + (slot)] += t_now - prof_last;     \
-    prof_last = t_now;                                                 \
-  } while (0)
-#else
-#define FA_TM(role, iter, slot) FA_TR(lane == 0, role, iter, slot)
-#endif
 
 namespace fa {
 
@@ -146,43 +101,16 @@ __device__ __forceinline__ ItemGeom decode_item(int item, const FwdParams& p) {
   return g;
 }
 
-// 2^x for a pair of scores on the FMA pipe: round-to-nearest split x = n + f with f in [-0.5, 0.5],
-// degree-3 minimax polynomial for 2^f (relative error 7.5e-5, below half an fp16 ulp of P), and n
-// added into the exponent field. x is clamped at -120 so the exponent cannot wrap.
-__device__ __forceinline__ void exp2_poly_pair(float x0, float x1, float& e0, float& e1) {
-  const float kMagic = 12582912.f;  // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
-  x0 = fmaxf(x0, -120.f);
-  x1 = fmaxf(x1, -120.f);
-  const uint64_t x2 = f2_pack(x0, x1);
-  const uint64_t t2 = f2_add(x2, f2_pack(kMagic, kMagic));
-  const uint64_t n2 = f2_add(t2, f2_pack(-kMagic, -kMagic));
-  const uint64_t f2 = f2_fma(n2, f2_pack(-1.f, -1.f), x2);
-  uint64_t r2 = f2_fma(f2, f2_pack(0.05517147481441498f, 0.05517147481441498f),
-                       f2_pack(0.2426111102104187f, 0.2426111102104187f));
-  r2 = f2_fma(r2, f2, f2_pack(0.6932610273361206f, 0.6932610273361206f));
-  r2 = f2_fma(r2, f2, f2_pack(0.9999280571937561f, 0.9999280571937561f));
-  float t0, t1, r0, r1;
-  f2_unpack(t2, t0, t1);
-  f2_unpack(r2, r0, r1);
-  e0 = __uint_as_float(__float_as_uint(r0) + (__float_as_uint(t0) << 23));
-  e1 = __uint_as_float(__float_as_uint(r1) + (__float_as_uint(t1) << 23));
-}
-
 // exp2 of 64 scores (32 pairs) -> 32 packed fp16x2 words; adds the exponentials into two
 // (even, odd) pairs of partial row sums.
-template <bool kAllowPoly>
 __device__ __forceinline__ void exp_half_tile(const float* sc, uint64_t scale2, uint64_t negms2, uint32_t (&pk)[32],
                                               uint64_t& lsum_a, uint64_t& lsum_b) {
 #pragma unroll
   for (int c = 0; c < 32; ++c) {
     float x0, x1, e0, e1;
     f2_unpack(f2_fma(f2_pack(sc[2 * c], sc[2 * c + 1]), scale2, negms2), x0, x1);
-    if (kAllowPoly && (c % 8) < FA_EMU_PAIRS) {
-      exp2_poly_pair(x0, x1, e0, e1);
-    } else {
-      e0 = ex2_approx(x0);
-      e1 = ex2_approx(x1);
-    }
+    e0 = ex2_approx(x0);
+    e1 = ex2_approx(x1);
     if (c & 1) lsum_b = f2_add(lsum_b, f2_pack(e0, e1));
     else lsum_a = f2_add(lsum_a, f2_pack(e0, e1));
     pk[c] = pack_f16x2(e0, e1);
@@ -190,19 +118,14 @@ __device__ __forceinline__ void exp_half_tile(const float* sc, uint64_t scale2, 
 }
 
 // Same for 32 scores (16 pairs) -> the first 16 words of pk.
-template <bool kAllowPoly>
 __device__ __forceinline__ void exp_quarter_tile(const float* sc, uint64_t scale2, uint64_t negms2, uint32_t* pk,
                                                  uint64_t& lsum_a, uint64_t& lsum_b) {
 #pragma unroll
   for (int c = 0; c < 16; ++c) {
     float x0, x1, e0, e1;
     f2_unpack(f2_fma(f2_pack(sc[2 * c], sc[2 * c + 1]), scale2, negms2), x0, x1);
-    if (kAllowPoly && (c % 8) < FA_EMU_PAIRS) {
-      exp2_poly_pair(x0, x1, e0, e1);
-    } else {
-      e0 = ex2_approx(x0);
-      e1 = ex2_approx(x1);
-    }
+    e0 = ex2_approx(x0);
+    e1 = ex2_approx(x1);
     if (c & 1) lsum_b = f2_add(lsum_b, f2_pack(e0, e1));
     else lsum_a = f2_add(lsum_a, f2_pack(e0, e1));
     pk[c] = pack_f16x2(e0, e1);
@@ -339,24 +262,6 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         if (!mbar_wait_warp(&s_full[s], n_s & 1, abort_flag)) { ok = false; break; }
         ++n_s;
         tc_fence_after();
-#ifdef FA_TRACE2
-        if (blockIdx.x == 0 && warp == 0 && lane == 0 && p.dbg != nullptr && n_s < 1300) {
-          long long* o = reinterpret_cast<long long*>(p.dbg) + 3 * (n_s - 1);
-          o[0] = clock64(); o[1] = item; o[2] = j;
-        }
-#endif
-        FA_TR(lane == 0, warp, j - j_lo, 0);
-#ifdef FA_FAKE_SOFTMAX  // bring-up only: measures the load + tensor pipeline without the softmax work
-        if (FA_FAKE_SOFTMAX > 0) {
-          const long long t_end = clock64() + FA_FAKE_SOFTMAX;
-          while (clock64() < t_end) {}
-        }
-        sAlpha[s * kBlockM + row_l] = 1.f;
-        __syncwarp();
-        if (lane == 0) { if (j != j_lo) mbar_arrive(&alpha_ready[s]); mbar_arrive(&p_full[s]); mbar_arrive(&p_full2[s]); }
-        l_run = 1.f;
-        continue;
-#endif
         const int kv0 = j * kBlockN;
         // One body, instantiated twice: tiles cut by a mask boundary (or by the end of the sequence) take the
         // per-element predicate, all others carry none of that code. (Blanking a cut tile in tensor memory first
@@ -374,7 +279,6 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           tmem_ld_fence(r1);
           tmem_ld_fence(r2);
           tmem_ld_fence(r3);
-          FA_TR(lane == 0, warp, j - j_lo, 1);
           float sc[kBlockN];
   #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -405,7 +309,7 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           uint32_t pk0[32], pk1[32];
           {
             const float neg_ms0 = -m_used * sl2;
-            exp_quarter_tile<!kMasked>(sc, scale2, f2_pack(neg_ms0, neg_ms0), pk0, lsum_a, lsum_b);
+            exp_quarter_tile(sc, scale2, f2_pack(neg_ms0, neg_ms0), pk0, lsum_a, lsum_b);
           }
           float mx0 = m_run, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
   #pragma unroll
@@ -431,24 +335,22 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             lsum_a = 0ull;
             lsum_b = 0ull;
             const float neg_ms1 = -m_used * sl2;
-            exp_quarter_tile<!kMasked>(sc, scale2, f2_pack(neg_ms1, neg_ms1), pk0, lsum_a, lsum_b);
+            exp_quarter_tile(sc, scale2, f2_pack(neg_ms1, neg_ms1), pk0, lsum_a, lsum_b);
           }
           // (no hand-over on the first tile of an item: there is nothing to rescale yet, and the correction warps
           // may still be in the previous item's epilogue)
           sAlpha[s * kBlockM + row_l] = alpha;
           __syncwarp();
           if (lane == 0 && j != j_lo) mbar_arrive(&alpha_ready[s]);
-          FA_TR(lane == 0, warp, j - j_lo, 2);
           const float neg_ms = -m_used * sl2;
           const uint64_t negms2 = f2_pack(neg_ms, neg_ms);
-          exp_quarter_tile<!kMasked>(sc + 32, scale2, negms2, pk0 + 16, lsum_a, lsum_b);
+          exp_quarter_tile(sc + 32, scale2, negms2, pk0 + 16, lsum_a, lsum_b);
           tmem_st32(tS + 0, pk0);
           tmem_wait_st();
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&p_full[s]);  // P of keys 0..63 is in TMEM
-          FA_TR(lane == 0, warp, j - j_lo, 3);
-          exp_half_tile<!kMasked>(sc + 64, scale2, negms2, pk1, lsum_a, lsum_b);
+          exp_half_tile(sc + 64, scale2, negms2, pk1, lsum_a, lsum_b);
           tmem_st32(tS + 32, pk1);
           float l0, l1;
           f2_unpack(f2_add(lsum_a, lsum_b), l0, l1);
@@ -460,7 +362,6 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         };
         if (kv_tile_needs_mask(kv0, q_r0, q_r1, wl, wr, N)) tile_body(std::true_type{});
         else tile_body(std::false_type{});
-        FA_TR(lane == 0, warp, j - j_lo, 4);
       }
       if (!ok) break;
       sRowSum[s * kBlockM + row_l] = l_run;
@@ -502,7 +403,6 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         if (!mbar_wait_warp(&o_full[s], n_o[s] & 1, abort_flag)) { ok = false; return; }
         ++n_o[s];
         tc_fence_after();
-        FA_TR(lane == 0, warp, g.hi_all - g.lo_all - 1, s * 4 + 2);
         const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
         const int row = g.r0[s] + row_l;
         const uint32_t tO = tmem_addr(tmem_base, lane_base, s == 0 ? Cfg::kColO0 : Cfg::kColO1);
@@ -536,7 +436,6 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[s]);
         arrived_early[s] = true;
-        FA_TR(lane == 0, warp, g.hi_all - g.lo_all - 1, s * 4 + 3);
       };
       for (int j = g.lo_all; j < g.hi_all && ok; ++j) {
         // a stage that has run out of tiles is finished first, while the other stage is still in its softmax
@@ -553,7 +452,6 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           } else {
             if (!mbar_wait_warp(&alpha_ready[s], n_alpha[s] & 1, abort_flag)) { ok = false; break; }
             ++n_alpha[s];
-            FA_TR(lane == 0, warp, j - g.lo_all, s * 4 + 0);
             const float alpha = sAlpha[s * kBlockM + row_l];
             if (__any_sync(0xffffffffu, alpha != 1.f)) {
               tc_fence_after();
@@ -574,7 +472,6 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&p_full[s]);
-          FA_TR(lane == 0, warp, j - g.lo_all, s * 4 + 1);
         }
       }
       if (!ok) break;
@@ -600,10 +497,6 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       uint32_t n_p[2] = {0, 0}, n_q[2] = {0, 0};
       uint32_t n_items = 0;
       bool ok = true;
-#ifdef FA_PROF
-      uint32_t prof_acc[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-      uint32_t prof_last = static_cast<uint32_t>(clock());
-#endif
       while (ok) {
         ItemGeom g;
         const int item = take_item(n_items, g);
@@ -637,13 +530,9 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             const uint32_t colO = (s == 0) ? Cfg::kColO0 : Cfg::kColO1;
             if (act_j) {  // O_s += P_s(j) V_j, in two halves of 64 keys as P arrives
               const uint64_t vdesc = vdesc0 + ((kv_addr + slot_v * Cfg::kTileBytes) >> 4);
-              FA_TM(12, j - g.lo_all + 1, s * 4 + 0);
               if (!v_seen && !mbar_wait_warp(&kv_full[slot_v], par_v, abort_flag)) { ok = false; return; }
-#ifndef FA_FAKE_NOWAIT  // (bring-up only: lets the issuer run without the softmax hand-shake)
               if (!mbar_wait_warp(&p_full[s], n_p[s] & 1, abort_flag)) { ok = false; return; }
-#endif
               tc_fence_after();
-              FA_TM(12, j - g.lo_all + 1, s * 4 + 1);
               if (elect_one()) {
                 umma_ts(tmem_base + colO, tmem_base + colS, vdesc, idesc_pv, (kInterior || j > g.lo[s]) ? 1u : 0u);
 #pragma unroll
@@ -651,13 +540,9 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                   umma_ts(tmem_base + colO, tmem_base + colS + kk * 8, vdesc + kk * (2048 >> 4), idesc_pv, 1u);
               }
               __syncwarp();
-              FA_TM(12, j - g.lo_all + 1, s * 4 + 2);
-#ifndef FA_FAKE_NOWAIT
               if (!mbar_wait_warp(&p_full2[s], n_p[s] & 1, abort_flag)) { ok = false; return; }
-#endif
               ++n_p[s];
               tc_fence_after();
-              FA_TM(12, j - g.lo_all + 1, s * 4 + 3);
               if (elect_one()) {
 #pragma unroll
                 for (int kk = 4; kk < 8; ++kk)
@@ -666,7 +551,6 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 if (!kInterior && j + 1 == g.hi[s]) umma_commit(&o_full[s]);
               }
               __syncwarp();
-              FA_TM(14, j - g.lo_all + 1, s * 4 + 0);
             }
             if (act_n) {  // S_s = Q_s K_{j+1}^T
               if (!kInterior && j + 1 == g.lo[s]) {
@@ -675,7 +559,6 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
               }
               if (!k_seen && !mbar_wait_warp(&kv_full[slot_k], par_k, abort_flag)) { ok = false; return; }
               tc_fence_after();
-              FA_TM(14, j - g.lo_all + 1, s * 4 + 1);
               const uint64_t kdesc = kdesc0 + ((kv_addr + slot_k * Cfg::kTileBytes) >> 4);
               if (elect_one()) {
 #pragma unroll
@@ -688,7 +571,6 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 if (!kInterior && j + 2 == g.hi[s]) umma_commit(&q_empty[s]);
               }
               __syncwarp();
-              FA_TM(14, j - g.lo_all + 1, s * 4 + 2);
             }
           }
         };
@@ -707,12 +589,6 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           advance(ring_slot, ring_par, n);
         }
       }
-#ifdef FA_PROF
-      if (blockIdx.x == 0 && p.dbg != nullptr && lane == 0) {
-        long long* out = reinterpret_cast<long long*>(p.dbg) + 3 * 16;
-        for (int i = 0; i < 16; ++i) out[i] = prof_acc[i];
-      }
-#endif
     } else if (warp == 13 && lane == 0) {
       // ===================================================================================
       // TMA producer
@@ -744,9 +620,6 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         // claim the following item now; the value is not needed before this item's loads are issued
         next = static_cast<int>(gridDim.x) + atomicAdd(p.sched, 1);
         if (next >= p.num_items) next = -1;
-#ifdef FA_TRACE3
-        const uint32_t n_items = n_pub;
-#endif
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
           if (g.r1[s] < g.r0[s]) continue;
@@ -754,19 +627,12 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           ++n_q[s];
           mbar_arrive_expect_tx(&q_full[s], Cfg::kTileBytes);
           tma_load_4d(sQ + s * Cfg::kTileBytes, &mapQ, &q_full[s], 0, g.r0[s], 0, g.bh);
-          FA_TR(true, 13, 0, 4 + s);
         }
         for (int j = g.lo_all; j < g.hi_all && ok; ++j) {
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
             const uint32_t slot = it % Cfg::kStages;
             if (!mbar_wait(&kv_empty[slot], ((it / Cfg::kStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
-            FA_TR(true, 13, j - g.lo_all, t * 2 + 0);
-#ifdef FA_FAKE_LOADS  // bring-up only: after the ring has been filled once, tiles "arrive" without being loaded
-            if (it >= Cfg::kStages) {
-              mbar_arrive(&kv_full[slot]);
-            } else
-#endif
 #ifdef FA_TEST_WITHHOLD_LOAD  // test build only: CTA 0 never loads its fourth tile, so that a bounded wait runs out
             if (blockIdx.x == 0 && (p.variant & 2) != 0 && it == 3) {
               ++it;
@@ -791,11 +657,7 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
   tc_fence_before();
   __syncthreads();
   if (tid == 0) {
-#ifdef FA_WAIT_DEBUG
-    if (*abort_flag != 0) atomicCAS(p.status, 0, *abort_flag);
-#else
     if (*abort_flag != 0) atomicExch(p.status, 1);
-#endif
     // the last CTA to finish puts the scheduler words back to zero for the next launch
     if (atomicAdd(p.sched + 1, 1) == static_cast<int>(gridDim.x) - 1) {
       p.sched[0] = 0;

@@ -93,7 +93,8 @@ int flash_forward_multi_gpu(int num_slabs, const int* devices, const void* const
 /* Same operation with an explicit kernel choice, for tests and bring-up:
  *   kernel  0 = default (warp-specialised persistent kernel), 1 = serial one-tile-per-CTA kernel,
  *           2 = CTA-pair kernel (cta_group::2 MMA over a cluster of two CTAs, head_dim 128 only)
- *   variant kernel-specific switches (serial kernel: bit0 stages P in shared memory)
+ *   variant kernel-specific switches (serial kernel: bit0 stages P in shared memory; bit1 is read only by the
+ *           test build of the library, where it makes one CTA withhold a tile so that a wait runs out)
  *   dbg     optional device buffer of 128*128 + 128*head_dim floats receiving the raw first
  *           score tile and first P.V product of q tile 0 / head 0 (serial kernel), else NULL
  * No counterpart in the reference (it has a single kernel).

@@ -28,7 +28,7 @@ CASES = [
     ("n384d64_causal_w128", 1, 1, 384, 64, 1, 128, 0, "normal"),          # causal + window, as config 4 combines them
     ("n256d64_w100", 1, 1, 256, 64, 0, 100, 0, "normal"),                 # symmetric window, not a multiple of 128
     ("n256d128_causal_w37", 1, 1, 256, 128, 1, 37, 0, "normal"),
-    ("n256d64_causal_alibi", 1, 2, 256, 64, 1, -1, 1, "normal"),          # oracle-only: ALiBi is outside the CUDA path
+    ("n256d64_causal_alibi", 1, 2, 256, 64, 1, -1, 1, "normal"),          # the reference's ALiBi bias (flash_forward_alibi / Has_alibi)
     ("n256d64_uniform0_10", 1, 1, 256, 64, 0, -1, 0, "uniform"),          # the reference's own smoke distribution
 ]
 
