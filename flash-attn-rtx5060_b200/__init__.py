@@ -26,6 +26,8 @@ EXPORTS = (
     "flash_forward_ex",
     "flash_forward_alibi",
     "flash_forward_lse",
+    "flash_forward_dropout",
+    "flash_forward_dropout_keep_probability",
     "flash_forward_multi_gpu",
     "flash_forward_host",
     "flash_forward_host_workspace_bytes",
@@ -64,6 +66,10 @@ def lib():
     L.flash_forward_alibi.restype = i
     L.flash_forward_lse.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, f, i, i, i, vp, vp]
     L.flash_forward_lse.restype = i
+    L.flash_forward_dropout.argtypes = [vp, vp, vp, vp, i, i, i, i, f, i, i, i, vp, f, ctypes.c_ulonglong, vp]
+    L.flash_forward_dropout.restype = i
+    L.flash_forward_dropout_keep_probability.argtypes = [f]
+    L.flash_forward_dropout_keep_probability.restype = ctypes.c_double
     pp = ctypes.POINTER(vp)
     L.flash_forward_multi_gpu.argtypes = [i, ctypes.POINTER(i), pp, pp, pp, pp, ctypes.POINTER(i), i, i, f, i, i, i, pp, i]
     L.flash_forward_multi_gpu.restype = i
@@ -179,11 +185,12 @@ def run_flash_attention(B, N, S, d, Q, K, V, O, L=None, M=None, Is_dropout=False
 
 
 def attention_forward(q, k, v, causal=False, window_left=-1, window_right=-1, softmax_scale=0.0, out=None, kernel=0,
-                      variant=0, alibi_slopes=None, return_lse=False):
+                      variant=0, alibi_slopes=None, return_lse=False, dropout_p=0.0, seed=0):
     """Convenience wrapper for torch CUDA tensors of shape [B, H, N, d], fp16, contiguous.
 
     torch is used for device memory and the current stream only; the computation is the library's.
     With return_lse the result is (out, lse), lse a float32 [B, H, N] tensor (flash_forward_lse).
+    With dropout_p > 0 the call is flash_forward_dropout(dropout_p, seed).
     """
     import torch
 
@@ -196,6 +203,15 @@ def attention_forward(q, k, v, causal=False, window_left=-1, window_right=-1, so
     with torch.cuda.device(q.device):
         if alibi_slopes is not None:
             assert alibi_slopes.is_cuda and alibi_slopes.dtype == torch.float32 and alibi_slopes.numel() == H
+        if dropout_p > 0.0:
+            assert kernel == 0 and variant == 0 and not return_lse
+            rc = lib().flash_forward_dropout(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, H, N, d,
+                                             softmax_scale, int(bool(causal)), window_left, window_right,
+                                             None if alibi_slopes is None else alibi_slopes.data_ptr(), dropout_p,
+                                             seed, stream)
+            if rc != FA_OK:
+                _raise(rc)
+            return out
         if return_lse:
             assert kernel == 0 and variant == 0
             lse = torch.empty((B, H, N), device=q.device, dtype=torch.float32)

@@ -13,6 +13,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 
 #include "../../include/flash_forward_b200.h"
@@ -71,7 +72,7 @@ struct DeviceState {
   cudaEvent_t slot_done[kSchedSlots] = {};     // recorded behind the last launch that used the pair
   cudaStream_t slot_stream[kSchedSlots] = {};  // the stream of that launch
   bool slot_used[kSchedSlots] = {};
-  bool attr_set[12] = {};
+  bool attr_set[16] = {};
 };
 
 // Hands out the scheduler words for one launch on `st`. Call with s->mu held; `*slot_out` is passed to
@@ -192,31 +193,33 @@ int launch_pair_ahead(DeviceState* s, const void* q, const void* k, const void* 
   return FA_OK;
 }
 
-template <int D, bool kAlibi, bool kLse>
+template <int D, bool kAlibi, bool kLse, bool kDropout = false>
 int launch_persistent_as(DeviceState* s, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                          const fa::FwdParams& p, cudaStream_t st) {
   using Cfg = fa::PersistentCfg<D>;
-  // attribute slots 2..5 and 8..11: one per instantiation
-  constexpr int slot = (kLse ? 8 : 2) + (kAlibi ? 2 : 0) + (D == 64 ? 0 : 1);
-  int rc = ensure_smem_attr(s, slot, fa::fwd_persistent_kernel<D, kAlibi, kLse>, Cfg::kSmemBytes);
+  // attribute slots 2..5, 8..11 and 12..15: one per instantiation
+  constexpr int slot = (kDropout ? 12 : (kLse ? 8 : 2)) + (kAlibi ? 2 : 0) + (D == 64 ? 0 : 1);
+  int rc = ensure_smem_attr(s, slot, fa::fwd_persistent_kernel<D, kAlibi, kLse, kDropout>, Cfg::kSmemBytes);
   if (rc != FA_OK) return rc;
   int grid = p.num_items < s->num_sms ? p.num_items : s->num_sms;
   fa::FwdParams pp = p;
   std::lock_guard<std::mutex> lk(s->mu);
   int sched_slot = 0;
   if ((rc = sched_acquire(s, st, &pp.sched, &sched_slot)) != FA_OK) return rc;
-  fa::fwd_persistent_kernel<D, kAlibi, kLse><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mk, mv, pp);
+  fa::fwd_persistent_kernel<D, kAlibi, kLse, kDropout><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mk, mv, pp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail_cuda("launch fwd_persistent_kernel", e);
   return sched_release(s, st, sched_slot);
 }
 
-// The ALiBi bias and the log-sum-exp output are compiled in only where asked for, so the plain
-// forward carries neither the per-element bias arithmetic nor the extra live values.
+// The ALiBi bias, the log-sum-exp output and dropout are compiled in only where asked for, so the plain
+// forward carries none of their arithmetic or live values.
 template <int D>
 int launch_persistent(DeviceState* s, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                      const fa::FwdParams& p, cudaStream_t st) {
+                      const fa::FwdParams& p, cudaStream_t st, bool dropout) {
   const bool alibi = p.alibi_slopes != nullptr, lse = p.lse != nullptr;
+  if (dropout) return alibi ? launch_persistent_as<D, true, false, true>(s, mq, mk, mv, p, st)
+                            : launch_persistent_as<D, false, false, true>(s, mq, mk, mv, p, st);
   if (alibi) return lse ? launch_persistent_as<D, true, true>(s, mq, mk, mv, p, st)
                         : launch_persistent_as<D, true, false>(s, mq, mk, mv, p, st);
   return lse ? launch_persistent_as<D, false, true>(s, mq, mk, mv, p, st)
@@ -409,7 +412,7 @@ int flash_forward_kv_range(int seqlen, int is_causal, int window_left, int windo
 static int forward_impl(const void* q, const void* k, const void* v, void* o, int batch, int heads, int seqlen,
                         int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,
                         const float* alibi_slopes, void* stream, int kernel, int variant, float* dbg,
-                        float* lse = nullptr) {
+                        float* lse = nullptr, float dropout_prob = 0.f, unsigned long long seed = 0) {
   if (!q || !k || !v || !o) return fail(FA_INVALID_ARG, "null tensor pointer");
   if (reinterpret_cast<uintptr_t>(lse) & 3) return fail(FA_INVALID_ARG, "lse must be 4-byte aligned");
   if (lse && kernel != 0) return fail(FA_UNSUPPORTED, "only the default kernel writes the log-sum-exp");
@@ -423,6 +426,12 @@ static int forward_impl(const void* q, const void* k, const void* v, void* o, in
   if (kernel < 0 || kernel > 2) return fail(FA_INVALID_ARG, "kernel must be 0 (default), 1 (serial) or 2 (CTA pair)");
   if (kernel == 2 && head_dim != 128) return fail(FA_UNSUPPORTED, "the CTA-pair kernel needs head_dim 128");
   if (!(softmax_scale == softmax_scale)) return fail(FA_INVALID_ARG, "softmax_scale is NaN");
+  if (!(dropout_prob >= 0.f && dropout_prob <= 1.f)) return fail(FA_INVALID_ARG, "dropout_prob must lie in [0, 1]");
+  // keep threshold in 1/256 steps (nearest); a probability below 1/512 keeps everything and takes the plain kernel
+  const unsigned keep_thr = (unsigned)rintf(256.f * (1.f - dropout_prob));
+  const bool dropout = keep_thr < 256u;
+  if (dropout && kernel != 0) return fail(FA_UNSUPPORTED, "only the default kernel has dropout");
+  if (dropout && lse) return fail(FA_UNSUPPORTED, "dropout and the log-sum-exp output are not combined");
 
   DeviceState* s = nullptr;
   int rc = device_state(&s);
@@ -447,6 +456,10 @@ static int forward_impl(const void* q, const void* k, const void* v, void* o, in
   p.alibi_slopes = alibi_slopes;
   p.lse = lse;
   p.heads = heads;
+  p.drop_keep_thr = dropout ? keep_thr : 256u;
+  p.seed_lo = (unsigned)(seed & 0xffffffffull);
+  p.seed_hi = (unsigned)(seed >> 32);
+  p.drop_scale = (dropout && keep_thr > 0) ? 256.f / (float)keep_thr : (dropout ? 0.f : 1.f);
   p.num_q_pairs = (seqlen + 2 * fa::kBlockM - 1) / (2 * fa::kBlockM);
   if ((long long)bh * p.num_q_pairs > 0x7fffffffLL) return fail(FA_INVALID_ARG, "too many work items");
   p.num_items = bh * p.num_q_pairs;
@@ -462,7 +475,8 @@ static int forward_impl(const void* q, const void* k, const void* v, void* o, in
   if (kernel == 1) {
     return head_dim == 64 ? launch_serial<64>(s, mq, mk, mv, p, st) : launch_serial<128>(s, mq, mk, mv, p, st);
   }
-  return head_dim == 64 ? launch_persistent<64>(s, mq, mk, mv, p, st) : launch_persistent<128>(s, mq, mk, mv, p, st);
+  return head_dim == 64 ? launch_persistent<64>(s, mq, mk, mv, p, st, dropout)
+                        : launch_persistent<128>(s, mq, mk, mv, p, st, dropout);
 }
 
 int flash_forward_ex(const void* q, const void* k, const void* v, void* o, int batch, int heads, int seqlen,
@@ -493,6 +507,19 @@ int flash_forward_lse(const void* q, const void* k, const void* v, void* o, floa
   if (!lse) return fail(FA_INVALID_ARG, "lse is null");
   return forward_impl(q, k, v, o, batch, heads, seqlen, head_dim, softmax_scale, is_causal, window_left, window_right,
                       alibi_slopes, stream, 0, 0, nullptr, lse);
+}
+
+int flash_forward_dropout(const void* q, const void* k, const void* v, void* o, int batch, int heads, int seqlen,
+                          int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,
+                          const float* alibi_slopes, float dropout_prob, unsigned long long seed, void* stream) {
+  return forward_impl(q, k, v, o, batch, heads, seqlen, head_dim, softmax_scale, is_causal, window_left, window_right,
+                      alibi_slopes, stream, 0, 0, nullptr, nullptr, dropout_prob, seed);
+}
+
+double flash_forward_dropout_keep_probability(float dropout_prob) {
+  if (!(dropout_prob >= 0.f && dropout_prob <= 1.f)) return -1.0;
+  const unsigned keep_thr = (unsigned)rintf(256.f * (1.f - dropout_prob));
+  return keep_thr >= 256u ? 1.0 : keep_thr / 256.0;
 }
 
 int flash_forward_multi_gpu(int num_slabs, const int* devices, const void* const* q, const void* const* k,
@@ -546,8 +573,14 @@ int flash_forward_check(void* stream) {
 int run_flash_attention_c(int B, int N, int S, int d, void* Q, void* K, void* V, void* O, void* L, void* M,
                           int Is_dropout, int Is_causal, int Is_local, int Has_alibi, int window_size,
                           float* alibi_slopes, float dropout_prob, void* states) {
-  (void)L; (void)M; (void)dropout_prob; (void)states;
-  if (Is_dropout) return fail(FA_UNSUPPORTED, "dropout is outside this library's path");
+  (void)L; (void)M; (void)states;
+  // The reference draws from curand states that its driver seeds with 48 (src/main.cu:93-95) and that advance from
+  // call to call. Here the mask is a function of (seed, head, row, column); the seed starts at 48 and moves on with
+  // every call that uses dropout, so repeated calls draw fresh masks as they do in the reference.
+  static std::atomic<unsigned long long> dropout_calls{0};
+  if (Is_dropout && !(dropout_prob >= 0.f && dropout_prob <= 1.f)) return fail(FA_INVALID_ARG, "dropout_prob must lie in [0, 1]");
+  const float drop_p = Is_dropout ? dropout_prob : 0.f;
+  const unsigned long long seed = 48ull + (Is_dropout ? dropout_calls.fetch_add(1) : 0ull);
   if (Has_alibi && !alibi_slopes) return fail(FA_INVALID_ARG, "Has_alibi needs alibi_slopes");
   if (Is_local && window_size < 0) return fail(FA_INVALID_ARG, "Is_local needs window_size >= 0");
   const int wl = Is_local ? window_size : -1;
@@ -558,7 +591,7 @@ int run_flash_attention_c(int B, int N, int S, int d, void* Q, void* K, void* V,
   if ((e = cudaEventCreate(&t1)) != cudaSuccess) { cudaEventDestroy(t0); return fail_cuda("cudaEventCreate", e); }
   cudaEventRecord(t0, 0);
   int rc = forward_impl(Q, K, V, O, B, N, S, d, 0.f, Is_causal, wl, wr, Has_alibi ? alibi_slopes : nullptr, nullptr, 0,
-                        0, nullptr);
+                        0, nullptr, nullptr, drop_p, seed);
   cudaEventRecord(t1, 0);
   if (rc == FA_OK) rc = flash_forward_check(nullptr);
   float ms = 0.f;

@@ -36,6 +36,11 @@ struct FwdParams {
                      // visible keys of each row (-inf for a row without visible keys); nullptr = not written
                      // (persistent kernel only).
                      // The reference declares L/M outputs (src/flash_forward.h:602-603) but never writes them.
+  // dropout on the attention probabilities (persistent kernel, its own instantiation): element (b*h, i, j) is kept
+  // when byte (j % 16) of Philox-4x32-10(key = seed, counter = {j / 16, i, b*h, 0}) is below drop_keep_thr
+  unsigned drop_keep_thr;   // 1..255 = round(256 * (1 - p)); 0 = every element dropped
+  unsigned seed_lo, seed_hi;
+  float drop_scale;         // 256 / drop_keep_thr: the kept elements' 1 / (1 - p), folded into the epilogue
   int* sched;        // device scratch, two words that are 0 between launches: [0] next work item to
                      // hand out (beyond the first gridDim.x), [1] CTAs that have finished
 };

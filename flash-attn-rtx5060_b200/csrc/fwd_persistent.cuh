@@ -132,7 +132,47 @@ __device__ __forceinline__ void exp_quarter_tile(const float* sc, uint64_t scale
   }
 }
 
-template <int D, bool kAlibi, bool kLse = false>
+// Philox-4x32 with 10 rounds (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3"): a keyed bijection of a
+// 128-bit counter. Stateless, so the keep mask of dropout depends only on (seed, head, row, column) and is the same
+// whatever tile shape or schedule computes it. (The reference keeps ONE generator state per q tile, copies it into
+// every thread of the CTA, so all threads draw the same numbers, and stores it back: src/flash_forward.h:185-186,
+// :248-265, :361-363. That flaw is not reproduced.)
+__device__ __forceinline__ void philox4x32_10(uint32_t k0, uint32_t k1, uint32_t c0, uint32_t c1, uint32_t c2,
+                                              uint32_t c3, uint32_t (&out)[4]) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    c0 = hi1 ^ c1 ^ k0;
+    c1 = lo1;
+    c2 = hi0 ^ c3 ^ k1;
+    c3 = lo0;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+
+// Zeroes the dropped elements of 32 packed fp16 pairs (64 consecutive columns starting at global column `col0`, a
+// multiple of 16) of query row `row` of head `bh`. One Philox call serves 16 columns: byte t of its 16 output bytes
+// (little endian over the four words) decides column 16 * block + t.
+__device__ __forceinline__ void dropout_mask_64(uint32_t (&pk)[32], const FwdParams& p, int bh, int row, int col0) {
+  const uint32_t thr4 = p.drop_keep_thr * 0x01010101u;
+#pragma unroll
+  for (int blk = 0; blk < 4; ++blk) {
+    uint32_t r[4];
+    philox4x32_10(p.seed_lo, p.seed_hi, static_cast<uint32_t>(col0 / 16 + blk), static_cast<uint32_t>(row),
+                  static_cast<uint32_t>(bh), 0u, r);
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const uint32_t keep = __vcmpltu4(r[w], thr4);                // 0xff in every byte below the threshold
+      pk[blk * 8 + 2 * w] &= __byte_perm(keep, 0u, 0x1100);        // columns 4w, 4w+1
+      pk[blk * 8 + 2 * w + 1] &= __byte_perm(keep, 0u, 0x3322);    // columns 4w+2, 4w+3
+    }
+  }
+}
+
+template <int D, bool kAlibi, bool kLse = false, bool kDropout = false>
 __global__ void __launch_bounds__(512, 1)
 fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                       const __grid_constant__ CUtensorMap mapV, const FwdParams p) {
@@ -345,12 +385,14 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           const float neg_ms = -m_used * sl2;
           const uint64_t negms2 = f2_pack(neg_ms, neg_ms);
           exp_quarter_tile(sc + 32, scale2, negms2, pk0 + 16, lsum_a, lsum_b);
+          if (kDropout) dropout_mask_64(pk0, p, g.bh, row, kv0);  // the row sum keeps every exponential
           tmem_st32(tS + 0, pk0);
           tmem_wait_st();
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&p_full[s]);  // P of keys 0..63 is in TMEM
           exp_half_tile(sc + 64, scale2, negms2, pk1, lsum_a, lsum_b);
+          if (kDropout) dropout_mask_64(pk1, p, g.bh, row, kv0 + 64);
           tmem_st32(tS + 32, pk1);
           float l0, l1;
           f2_unpack(f2_add(lsum_a, lsum_b), l0, l1);
@@ -403,7 +445,7 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         if (!mbar_wait_warp(&o_full[s], n_o[s] & 1, abort_flag)) { ok = false; return; }
         ++n_o[s];
         tc_fence_after();
-        const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+        const float inv_l = ((l > 0.f) ? 1.f / l : 0.f) * (kDropout ? p.drop_scale : 1.f);
         const int row = g.r0[s] + row_l;
         const uint32_t tO = tmem_addr(tmem_base, lane_base, s == 0 ? Cfg::kColO0 : Cfg::kColO1);
         __half* orow = p.O + (static_cast<size_t>(g.bh) * N + row) * D;

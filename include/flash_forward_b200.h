@@ -20,7 +20,7 @@ extern "C" {
 enum {
   FA_OK = 0,
   FA_INVALID_ARG = 1,    /* null or misaligned pointer, non-positive size */
-  FA_UNSUPPORTED = 2,    /* head_dim not 64/128, dropout, device is not sm_100 */
+  FA_UNSUPPORTED = 2,    /* head_dim not 64/128, a combination a kernel lacks, device is not sm_100 */
   FA_CUDA_ERROR = 3,     /* a CUDA runtime/driver call failed; see flash_forward_last_error() */
   FA_DEVICE_TIMEOUT = 4  /* a bounded wait inside the kernel gave up (status word set) */
 };
@@ -76,6 +76,30 @@ int flash_forward_lse(const void* q, const void* k, const void* v, void* o, floa
                       int seqlen, int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,
                       const float* alibi_slopes, void* stream);
 
+/* The forward with dropout on the attention probabilities, the reference's Is_dropout / dropout_prob
+ * (src/flash_forward.h:248-265): after the softmax, each probability is dropped with probability p or
+ * scaled by 1/(1-p); the softmax normalisation itself uses all probabilities.
+ *
+ * The keep mask is a pure function of (seed, batch*heads index, query row, key column): a key column is
+ * kept when its byte of Philox-4x32-10(key = seed, counter = {column / 16, row, batch*heads index, 0}) is
+ * below round(256 * (1 - p)). p is therefore applied in steps of 1/256 (flash_forward_dropout_keep_probability()
+ * returns the keep probability actually used); p < 1/512 runs the plain forward, bit for bit. The same seed
+ * gives the same mask on any GPU and for any sharding of the (batch, head) axis only if the caller passes whole
+ * tensors; a slab call numbers its heads from 0.
+ *
+ * What differs from the reference, on purpose: the reference holds one curand state per q tile, copies it into
+ * every thread of the CTA (all threads draw the same numbers) and writes it back (src/flash_forward.h:185-186,
+ * :361-363; src/init_curand_states.h:7-14); it skips its own verification when dropout is on (src/main.cu:103).
+ * Its random stream is not reproduced; the statistics and the arithmetic are.
+ * alibi_slopes may be NULL. All other arguments as for flash_forward(). */
+int flash_forward_dropout(const void* q, const void* k, const void* v, void* o, int batch, int heads, int seqlen,
+                          int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,
+                          const float* alibi_slopes, float dropout_prob, unsigned long long seed, void* stream);
+
+/* Keep probability flash_forward_dropout() uses for `dropout_prob` (a multiple of 1/256; 1.0 when nothing is
+ * dropped), or -1 when dropout_prob is outside [0, 1]. Needs no GPU. */
+double flash_forward_dropout_keep_probability(float dropout_prob);
+
 /* Several GPUs from one host thread. Every (batch, head) is an independent problem (the reference's CPU
  * path loops over them, src/main.cu:179-186, and on its GPU a work item touches only its own head's
  * rows, src/flash_forward.h:128,:134), so the heads are cut into slabs and each slab runs on its own
@@ -130,7 +154,9 @@ int flash_forward_check(void* stream);
  *   Is_causal -> window_right = 0 (both masks apply when both flags are set, mask.h:15,:43)
  *   L, M      -> ignored (the reference never reads them)
  *   Has_alibi -> alibi_slopes (device, one float per head) is applied as in flash_forward_alibi()
- *   Is_dropout -> FA_UNSUPPORTED (outside this library's path)
+ *   Is_dropout -> flash_forward_dropout() with dropout_prob; `states` is ignored (the reference's curand states
+ *                 are seeded with 48 by its driver, src/main.cu:93-95, and advance from call to call: here the
+ *                 seed starts at 48 and is incremented by every call that uses dropout)
  * Unlike the reference it runs on the current device and returns a status instead of exiting. */
 int run_flash_attention_c(int B, int N, int S, int d, void* Q, void* K, void* V, void* O, void* L, void* M,
                           int Is_dropout, int Is_causal, int Is_local, int Has_alibi, int window_size,

@@ -25,6 +25,12 @@
  *     sum still adds its products in the reference's k order.
  * The window here is two-sided (left, right) because the library's ABI is; the reference's
  * symmetric window is left == right == w.
+ *
+ * Dropout (oracle_attention_forward_dropout): the reference's CPU function has none, and the
+ * reference skips its check when dropout is on (src/main.cu:103), so this part is NOT pinned by
+ * the reference. It restates what the reference's kernel does to P (src/flash_forward.h:248-265:
+ * after the softmax, drop with probability p, else scale by 1/(1-p)) on top of the steps above,
+ * with the library's documented keep rule (Philox-4x32-10, see include/flash_forward_b200.h).
  */
 #include <math.h>
 #include <pthread.h>
@@ -101,7 +107,35 @@ typedef struct {
   int causal, wl, wr;
   float slope;
   int use_alibi;
+  /* dropout: keep_thr in 0..255 (256 = off), the head's index in the flattened (batch, head) axis */
+  unsigned keep_thr;
+  uint64_t seed;
+  unsigned bh;
 } HeadCtx;
+
+/* Philox-4x32 with 10 rounds (Salmon, Moraes, Dror, Shaw 2011), written from the published description. */
+static void philox4x32_10(uint32_t k0, uint32_t k1, uint32_t c[4]) {
+  for (int r = 0; r < 10; ++r) {
+    const uint64_t p0 = (uint64_t)0xD2511F53u * c[0];
+    const uint64_t p1 = (uint64_t)0xCD9E8D57u * c[2];
+    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c[1] ^ k0;
+    const uint32_t n1 = (uint32_t)p1;
+    const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c[3] ^ k1;
+    const uint32_t n3 = (uint32_t)p0;
+    c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+}
+
+/* key column j of query row i of head bh is kept when byte (j % 16) of the block's 16 random bytes is below keep_thr */
+static int dropout_keep(uint64_t seed, unsigned bh, int i, int j, unsigned keep_thr) {
+  uint32_t c[4] = {(uint32_t)(j / 16), (uint32_t)i, bh, 0u};
+  philox4x32_10((uint32_t)seed, (uint32_t)(seed >> 32), c);
+  const unsigned t = (unsigned)(j % 16);
+  const unsigned byte = (c[t / 4] >> (8 * (t % 4))) & 0xffu;
+  return byte < keep_thr;
+}
 
 static void attend_row(const HeadCtx* c, int i, float* s, float* acc, uint16_t* out_row) {
   const int N = c->N, d = c->d;
@@ -143,7 +177,13 @@ static void attend_row(const HeadCtx* c, int i, float* s, float* acc, uint16_t* 
     s[j] = expf(s[j] - mx);
     sum += s[j];
   }
-  for (int j = 0; j < n; ++j) s[j] = round_h(s[j] / sum);
+  if (c->keep_thr < 256u) { /* dropout on the normalised probabilities */
+    const float keep_scale = c->keep_thr ? 256.0f / (float)c->keep_thr : 0.0f;
+    for (int j = 0; j < n; ++j)
+      s[j] = dropout_keep(c->seed, c->bh, i, lo + j, c->keep_thr) ? round_h(s[j] / sum * keep_scale) : 0.0f;
+  } else {
+    for (int j = 0; j < n; ++j) s[j] = round_h(s[j] / sum);
+  }
   /* step 5 */
   for (int k = 0; k < d; ++k) acc[k] = 0.0f;
   for (int j = 0; j < n; ++j) {
@@ -186,7 +226,7 @@ int oracle_attention_rows(const uint16_t* q, const uint16_t* k, const uint16_t* 
   float* s = (float*)malloc((size_t)N * sizeof(float));
   float* acc = (float*)malloc((size_t)d * sizeof(float));
   if (!s || !acc) { free(s); free(acc); free(Kt); free(Vf); return -1; }
-  HeadCtx c = {q, Kt, Vf, N, d, scale, causal, window_left, window_right, slope, use_alibi};
+  HeadCtx c = {q, Kt, Vf, N, d, scale, causal, window_left, window_right, slope, use_alibi, 256u, 0, 0};
   for (int r = 0; r < nrows; ++r) attend_row(&c, rows[r], s, acc, out + (size_t)r * d);
   free(s); free(acc); free(Kt); free(Vf);
   return 0;
@@ -202,6 +242,8 @@ typedef struct {
   const float* slopes;
   volatile int* next;
   int err;
+  unsigned keep_thr;
+  uint64_t seed;
 } Job;
 
 static void* worker(void* arg) {
@@ -216,7 +258,7 @@ static void* worker(void* arg) {
     float *Kt, *Vf;
     if (prepare_head(jb->K + bh * hs, jb->V + bh * hs, jb->N, jb->d, &Kt, &Vf) != 0) { jb->err = -1; break; }
     HeadCtx c = {jb->Q + bh * hs, Kt, Vf, jb->N, jb->d, jb->scale, jb->causal, jb->wl, jb->wr,
-                 jb->slopes ? jb->slopes[bh % jb->H] : 0.0f, jb->slopes != NULL};
+                 jb->slopes ? jb->slopes[bh % jb->H] : 0.0f, jb->slopes != NULL, jb->keep_thr, jb->seed, (unsigned)bh};
     for (int i = 0; i < jb->N; ++i) attend_row(&c, i, s, acc, jb->O + bh * hs + (size_t)i * jb->d);
     free(Kt); free(Vf);
   }
@@ -224,18 +266,16 @@ static void* worker(void* arg) {
   return NULL;
 }
 
-/* Attention of whole [B][H][N][d] fp16 tensors, one head at a time per thread.
- * alibi_slopes: H floats or NULL. Returns 0 or -1. */
-int oracle_attention_forward(const uint16_t* q, const uint16_t* k, const uint16_t* v, uint16_t* out, int B, int H,
-                             int N, int d, float scale, int causal, int window_left, int window_right,
-                             const float* alibi_slopes, int nthreads) {
+static int run_jobs(const uint16_t* q, const uint16_t* k, const uint16_t* v, uint16_t* out, int B, int H, int N, int d,
+                    float scale, int causal, int window_left, int window_right, const float* alibi_slopes, int nthreads,
+                    unsigned keep_thr, uint64_t seed) {
   if (nthreads < 1) nthreads = 1;
   if (nthreads > 256) nthreads = 256;
   volatile int next = 0;
   Job jobs[256];
   pthread_t th[256];
   for (int t = 0; t < nthreads; ++t) {
-    Job j = {q, k, v, out, B * H, H, N, d, scale, causal, window_left, window_right, alibi_slopes, &next, 0};
+    Job j = {q, k, v, out, B * H, H, N, d, scale, causal, window_left, window_right, alibi_slopes, &next, 0, keep_thr, seed};
     jobs[t] = j;
   }
   if (nthreads == 1) {
@@ -246,6 +286,30 @@ int oracle_attention_forward(const uint16_t* q, const uint16_t* k, const uint16_
   int err = 0;
   for (int t = 0; t < nthreads; ++t) { pthread_join(th[t], NULL); if (jobs[t].err) err = -1; }
   return err;
+}
+
+/* Attention of whole [B][H][N][d] fp16 tensors, one head at a time per thread.
+ * alibi_slopes: H floats or NULL. Returns 0 or -1. */
+int oracle_attention_forward(const uint16_t* q, const uint16_t* k, const uint16_t* v, uint16_t* out, int B, int H,
+                             int N, int d, float scale, int causal, int window_left, int window_right,
+                             const float* alibi_slopes, int nthreads) {
+  return run_jobs(q, k, v, out, B, H, N, d, scale, causal, window_left, window_right, alibi_slopes, nthreads, 256u, 0);
+}
+
+/* The same with dropout: keep_thr = round(256 * (1 - p)) in 0..255, seed as given to the library. */
+int oracle_attention_forward_dropout(const uint16_t* q, const uint16_t* k, const uint16_t* v, uint16_t* out, int B,
+                                     int H, int N, int d, float scale, int causal, int window_left, int window_right,
+                                     const float* alibi_slopes, int nthreads, unsigned keep_thr, uint64_t seed) {
+  return run_jobs(q, k, v, out, B, H, N, d, scale, causal, window_left, window_right, alibi_slopes, nthreads, keep_thr,
+                  seed);
+}
+
+/* The raw generator, for known-answer tests. ctr is read and overwritten with the output. */
+void oracle_philox4x32_10(uint32_t k0, uint32_t k1, uint32_t* ctr) { philox4x32_10(k0, k1, ctr); }
+
+/* The keep decision alone, for tests of the mask's statistics. */
+int oracle_dropout_keep(uint64_t seed, unsigned bh, int row, int col, unsigned keep_thr) {
+  return dropout_keep(seed, bh, row, col, keep_thr);
 }
 
 /* max and mean absolute difference of two fp16 arrays, compared in fp32 (the acceptance metric);

@@ -76,6 +76,34 @@ def attention(q, k, v, causal=False, window_left=-1, window_right=-1, scale=None
     return out.view(np.float16)
 
 
+def attention_dropout(q, k, v, dropout_p, seed, causal=False, window_left=-1, window_right=-1, scale=None,
+                      alibi_slopes=None, nthreads=None):
+    """Oracle attention with dropout on the probabilities (the library's documented keep rule: Philox-4x32-10, keep
+    threshold round(256 * (1 - p))). Not pinned by the reference, whose CPU function has no dropout."""
+    B, H, N, d = q.shape
+    q16, k16, v16 = _u16(q), _u16(k), _u16(v)
+    out = np.empty((B, H, N, d), dtype=np.uint16)
+    if scale is None:
+        scale = np.float32(1.0) / np.sqrt(np.float32(d))
+    sl = None if alibi_slopes is None else np.ascontiguousarray(alibi_slopes, dtype=np.float32)
+    nt = nthreads or min(os.cpu_count() or 1, B * H)
+    keep_thr = min(int(np.rint(np.float32(256.0) * (np.float32(1.0) - np.float32(dropout_p)))), 256)
+    fn = port().oracle_attention_forward_dropout
+    fn.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int] * 4 + [ctypes.c_float] + [ctypes.c_int] * 3 + [
+        ctypes.c_void_p, ctypes.c_int, ctypes.c_uint, ctypes.c_uint64]
+    rc = fn(q16.ctypes.data, k16.ctypes.data, v16.ctypes.data, out.ctypes.data, B, H, N, d, float(scale), int(causal),
+            window_left, window_right, sl.ctypes.data if sl is not None else None, nt, keep_thr, seed)
+    if rc != 0:
+        raise MemoryError("oracle_attention_forward_dropout failed")
+    return out.view(np.float16)
+
+
+def dropout_keep(seed, bh, row, col, keep_thr):
+    fn = port().oracle_dropout_keep
+    fn.argtypes = [ctypes.c_uint64, ctypes.c_uint, ctypes.c_int, ctypes.c_int, ctypes.c_uint]
+    return bool(fn(seed, bh, row, col, keep_thr))
+
+
 def attention_rows(q, k, v, rows, causal=False, window_left=-1, window_right=-1, scale=None, slope=None):
     """Oracle attention of selected query rows of ONE head: q, k, v fp16 [N, d] -> fp16 [len(rows), d]."""
     N, d = q.shape

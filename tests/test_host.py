@@ -49,8 +49,9 @@ def test_argument_errors_are_status_codes(pkg):
     assert b"head_dim" in L.flash_forward_last_error()
     assert L.flash_forward(ctypes.c_void_p(0x1008), p, p, p, 1, 1, 128, 64, 0.0, 0, -1, -1, None) == pkg.FA_INVALID_ARG
     assert L.flash_forward_ex(p, p, p, p, 1, 1, 128, 64, 0.0, 0, -1, -1, None, 7, 0, None) == pkg.FA_INVALID_ARG
-    # the reference's flags that are outside this path
-    assert L.run_flash_attention_c(1, 1, 128, 64, p, p, p, p, None, None, 1, 0, 0, 0, 0, None, 0.5, None) == pkg.FA_UNSUPPORTED
+    # dropout probability outside [0, 1]
+    assert L.run_flash_attention_c(1, 1, 128, 64, p, p, p, p, None, None, 1, 0, 0, 0, 0, None, 1.5, None) == pkg.FA_INVALID_ARG
+    assert L.flash_forward_dropout(p, p, p, p, 1, 1, 128, 64, 0.0, 0, -1, -1, None, -0.5, 0, None) == pkg.FA_INVALID_ARG
     # ALiBi without slopes is a caller error
     assert L.run_flash_attention_c(1, 1, 128, 64, p, p, p, p, None, None, 0, 0, 0, 1, 0, None, 0.0, None) == pkg.FA_INVALID_ARG
     assert L.flash_forward_alibi(p, p, p, p, 1, 1, 128, 64, 0.0, 0, -1, -1, None, None) == pkg.FA_INVALID_ARG
@@ -59,7 +60,7 @@ def test_argument_errors_are_status_codes(pkg):
     assert b"lse" in L.flash_forward_last_error()
     assert L.flash_forward_lse(p, p, p, p, ctypes.c_void_p(0x1002), 1, 1, 128, 64, 0.0, 0, -1, -1, None, None) == pkg.FA_INVALID_ARG
     with pytest.raises(pkg.FlashForwardError):
-        pkg.run_flash_attention(1, 1, 128, 64, 0x1000, 0x1000, 0x1000, 0x1000, Is_dropout=True)
+        pkg.run_flash_attention(1, 1, 128, 64, 0x1000, 0x1000, 0x1000, 0x1000, Is_dropout=True, dropout_prob=2.0)
     with pytest.raises(pkg.FlashForwardError):  # no slabs
         pkg.flash_forward_multi_gpu([], [], [], [], [], [], 128, 64)
 
