@@ -195,6 +195,7 @@ int launch_pair_ahead(DeviceState* s, const void* q, const void* k, const void* 
 
 template <int D, bool kAlibi, bool kLse, bool kDropout = false>
 int launch_persistent_as(DeviceState* s, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                         const CUtensorMap& mo,
                          const fa::FwdParams& p, cudaStream_t st) {
   using Cfg = fa::PersistentCfg<D>;
   // attribute slots 2..5, 8..11 and 12..15: one per instantiation
@@ -206,7 +207,7 @@ int launch_persistent_as(DeviceState* s, const CUtensorMap& mq, const CUtensorMa
   std::lock_guard<std::mutex> lk(s->mu);
   int sched_slot = 0;
   if ((rc = sched_acquire(s, st, &pp.sched, &sched_slot)) != FA_OK) return rc;
-  fa::fwd_persistent_kernel<D, kAlibi, kLse, kDropout><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mk, mv, pp);
+  fa::fwd_persistent_kernel<D, kAlibi, kLse, kDropout><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mk, mv, mo, pp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail_cuda("launch fwd_persistent_kernel", e);
   return sched_release(s, st, sched_slot);
@@ -216,14 +217,15 @@ int launch_persistent_as(DeviceState* s, const CUtensorMap& mq, const CUtensorMa
 // forward carries none of their arithmetic or live values.
 template <int D>
 int launch_persistent(DeviceState* s, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                      const CUtensorMap& mo,
                       const fa::FwdParams& p, cudaStream_t st, bool dropout) {
   const bool alibi = p.alibi_slopes != nullptr, lse = p.lse != nullptr;
-  if (dropout) return alibi ? launch_persistent_as<D, true, false, true>(s, mq, mk, mv, p, st)
-                            : launch_persistent_as<D, false, false, true>(s, mq, mk, mv, p, st);
-  if (alibi) return lse ? launch_persistent_as<D, true, true>(s, mq, mk, mv, p, st)
-                        : launch_persistent_as<D, true, false>(s, mq, mk, mv, p, st);
-  return lse ? launch_persistent_as<D, false, true>(s, mq, mk, mv, p, st)
-             : launch_persistent_as<D, false, false>(s, mq, mk, mv, p, st);
+  if (dropout) return alibi ? launch_persistent_as<D, true, false, true>(s, mq, mk, mv, mo, p, st)
+                            : launch_persistent_as<D, false, false, true>(s, mq, mk, mv, mo, p, st);
+  if (alibi) return lse ? launch_persistent_as<D, true, true>(s, mq, mk, mv, mo, p, st)
+                        : launch_persistent_as<D, true, false>(s, mq, mk, mv, mo, p, st);
+  return lse ? launch_persistent_as<D, false, true>(s, mq, mk, mv, mo, p, st)
+             : launch_persistent_as<D, false, false>(s, mq, mk, mv, mo, p, st);
 }
 
 // ---- host-buffer entry point -----------------------------------------------------------
@@ -308,6 +310,7 @@ int noalloc_state(NoAllocState** out) {
 
 template <int D>
 int launch_persistent_noalloc(NoAllocState* s, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                              const CUtensorMap& mo,
                               const fa::FwdParams& p, cudaStream_t st) {
   using Cfg = fa::PersistentCfg<D>;
   {
@@ -321,7 +324,7 @@ int launch_persistent_noalloc(NoAllocState* s, const CUtensorMap& mq, const CUte
     }
   }
   const int grid = p.num_items < s->num_sms ? p.num_items : s->num_sms;
-  fa::fwd_persistent_kernel<D, false><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mk, mv, p);
+  fa::fwd_persistent_kernel<D, false><<<grid, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mq, mk, mv, mo, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail_cuda("launch fwd_persistent_kernel", e);
   return FA_OK;
@@ -465,18 +468,19 @@ static int forward_impl(const void* q, const void* k, const void* v, void* o, in
   p.num_items = bh * p.num_q_pairs;
   p.head_group = pick_head_group(bh, seqlen, head_dim, p.causal, p.window_left, p.window_right, p.num_q_pairs, s->num_sms);
 
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mo;
   if ((rc = make_map(&mq, q, bh, seqlen, head_dim, fa::kBlockM)) != FA_OK) return rc;
   if ((rc = make_map(&mk, k, bh, seqlen, head_dim, fa::kBlockN)) != FA_OK) return rc;
   if ((rc = make_map(&mv, v, bh, seqlen, head_dim, fa::kBlockN)) != FA_OK) return rc;
+  if ((rc = make_map(&mo, o, bh, seqlen, head_dim, 32)) != FA_OK) return rc;  // one correction warp's rows per store
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (kernel == 2) return launch_pair_ahead(s, q, k, v, p, st);
   if (kernel == 1) {
     return head_dim == 64 ? launch_serial<64>(s, mq, mk, mv, p, st) : launch_serial<128>(s, mq, mk, mv, p, st);
   }
-  return head_dim == 64 ? launch_persistent<64>(s, mq, mk, mv, p, st, dropout)
-                        : launch_persistent<128>(s, mq, mk, mv, p, st, dropout);
+  return head_dim == 64 ? launch_persistent<64>(s, mq, mk, mv, mo, p, st, dropout)
+                        : launch_persistent<128>(s, mq, mk, mv, mo, p, st, dropout);
 }
 
 int flash_forward_ex(const void* q, const void* k, const void* v, void* o, int batch, int heads, int seqlen,
@@ -722,17 +726,18 @@ int flash_forward_noalloc(const void* q, const void* k, const void* v, void* o, 
   p.num_items = bh * pairs;
   p.head_group = pick_head_group(bh, seqlen, head_dim, p.causal, p.window_left, p.window_right, pairs, s->num_sms);
 
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mo;
   if ((rc = make_map(&mq, q, bh, seqlen, head_dim, fa::kBlockM)) != FA_OK) return rc;
   if ((rc = make_map(&mk, k, bh, seqlen, head_dim, fa::kBlockN)) != FA_OK) return rc;
   if ((rc = make_map(&mv, v, bh, seqlen, head_dim, fa::kBlockN)) != FA_OK) return rc;
+  if ((rc = make_map(&mo, o, bh, seqlen, head_dim, 32)) != FA_OK) return rc;  // one correction warp's rows per store
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // The slot keeps whatever the previous call left; status and both counters must start at zero.
   cudaError_t e = cudaMemsetAsync(words, 0, 4 * sizeof(int), st);
   if (e != cudaSuccess) return fail_cuda("cudaMemsetAsync(scratch slot)", e);
-  rc = head_dim == 64 ? launch_persistent_noalloc<64>(s, mq, mk, mv, p, st)
-                      : launch_persistent_noalloc<128>(s, mq, mk, mv, p, st);
+  rc = head_dim == 64 ? launch_persistent_noalloc<64>(s, mq, mk, mv, mo, p, st)
+                      : launch_persistent_noalloc<128>(s, mq, mk, mv, mo, p, st);
   if (rc != FA_OK || !wait) return rc;
 
   if ((e = cudaStreamSynchronize(st)) != cudaSuccess) return fail_cuda("cudaStreamSynchronize", e);

@@ -42,10 +42,14 @@ struct PersistentCfg {
   static constexpr int kThreads = 512;
   static constexpr int kTileBytes = kBlockN * D * 2;
   static constexpr int kPanelBytes = kBlockN * kPanel * 2;
-  static constexpr int kStages = (D == 128) ? 5 : 8;  // ring slots, each one K or one V tile
+  static constexpr int kStages = (D == 128) ? 4 : 8;  // ring slots, each one K or one V tile
   static constexpr int kOffQ = 0;
   static constexpr int kOffKV = 2 * kTileBytes;
-  static constexpr int kOffAlpha = kOffKV + kStages * kTileBytes;  // float[2][128]
+  // Output staging: each correction warp owns 32 rows, laid out [panel][row][64] with the 128-byte swizzle, the
+  // source of its TMA store.
+  static constexpr int kOffOut = kOffKV + kStages * kTileBytes;
+  static constexpr int kOutWarpBytes = 32 * D * 2;
+  static constexpr int kOffAlpha = kOffOut + 4 * kOutWarpBytes;  // float[2][128]
   static constexpr int kOffRowSum = kOffAlpha + 2 * kBlockM * 4;   // float[2][128]
   static constexpr int kOffBars = kOffRowSum + 2 * kBlockM * 4;
   static constexpr int kNumBars = 20 + 2 * kStages;
@@ -175,7 +179,8 @@ __device__ __forceinline__ void dropout_mask_64(uint32_t (&pk)[32], const FwdPar
 template <int D, bool kAlibi, bool kLse = false, bool kDropout = false>
 __global__ void __launch_bounds__(512, 1)
 fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
-                      const __grid_constant__ CUtensorMap mapV, const FwdParams p) {
+                      const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapO,
+                      const FwdParams p) {
   using Cfg = PersistentCfg<D>;
   extern __shared__ __align__(1024) uint8_t smem[];
 
@@ -240,6 +245,7 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     prefetch_tensormap(&mapQ);
     prefetch_tensormap(&mapK);
     prefetch_tensormap(&mapV);
+    prefetch_tensormap(&mapO);
   }
   tc_fence_before();
   __syncthreads();
@@ -422,6 +428,7 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     reg_dec<FA_REG_CORR>();
     const int row_l = tid & 127;
     const uint32_t lane_base = static_cast<uint32_t>(warp & 3) * 32u;
+    uint8_t* out_stage = smem + Cfg::kOffOut + (warp & 3) * Cfg::kOutWarpBytes;
     uint32_t n_alpha[2] = {0, 0}, n_l[2] = {0, 0}, n_o[2] = {0, 0};
     uint32_t n_items = 0;
     // The first P.V product of an item overwrites O, so it has to wait until the epilogue of the previous item
@@ -446,9 +453,12 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         ++n_o[s];
         tc_fence_after();
         const float inv_l = ((l > 0.f) ? 1.f / l : 0.f) * (kDropout ? p.drop_scale : 1.f);
-        const int row = g.r0[s] + row_l;
         const uint32_t tO = tmem_addr(tmem_base, lane_base, s == 0 ? Cfg::kColO0 : Cfg::kColO1);
-        __half* orow = p.O + (static_cast<size_t>(g.bh) * N + row) * D;
+        // The rows go to the warp's staging area and from there to global memory as one TMA store: issued as plain
+        // stores (each lane its own row, 16 bytes at a time) they kept the load/store unit busy for about 2000
+        // clocks per tile, and the barrier traffic of every other warp of the SM queued behind them.
+        if (lane == 0) tma_store_wait_read();  // the previous store of this warp has read the staging area
+        __syncwarp();
         // 16 columns at a time, the load of the next chunk in flight while this one is converted and stored.
         // (Rolled up: this path runs once per item and stage, and instructions that are rarely executed are
         // fetched slowly; unrolling it eightfold made the change-over between items slower, not faster.)
@@ -461,22 +471,31 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
           tmem_wait_ld();
           tmem_ld_fence16(cur);
           if (c + 1 < D / 16) tmem_ld16(tO + (c + 1) * 16, nxt);
-          if (row < N) {
+          // columns 16c .. 16c+15 are 16-byte units 2(c%4), 2(c%4)+1 of panel c/4; unit u of row r sits at u ^ (r%8)
+          uint8_t* prow = out_stage + (c >> 2) * (32 * 128) + lane * 128;
   #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-              uint4 v;
-              v.x = pack_f16x2(__uint_as_float(cur[i * 8 + 0]) * inv_l, __uint_as_float(cur[i * 8 + 1]) * inv_l);
-              v.y = pack_f16x2(__uint_as_float(cur[i * 8 + 2]) * inv_l, __uint_as_float(cur[i * 8 + 3]) * inv_l);
-              v.z = pack_f16x2(__uint_as_float(cur[i * 8 + 4]) * inv_l, __uint_as_float(cur[i * 8 + 5]) * inv_l);
-              v.w = pack_f16x2(__uint_as_float(cur[i * 8 + 6]) * inv_l, __uint_as_float(cur[i * 8 + 7]) * inv_l);
-              *reinterpret_cast<uint4*>(orow + c * 16 + i * 8) = v;
-            }
+          for (int i = 0; i < 2; ++i) {
+            uint4 v;
+            v.x = pack_f16x2(__uint_as_float(cur[i * 8 + 0]) * inv_l, __uint_as_float(cur[i * 8 + 1]) * inv_l);
+            v.y = pack_f16x2(__uint_as_float(cur[i * 8 + 2]) * inv_l, __uint_as_float(cur[i * 8 + 3]) * inv_l);
+            v.z = pack_f16x2(__uint_as_float(cur[i * 8 + 4]) * inv_l, __uint_as_float(cur[i * 8 + 5]) * inv_l);
+            v.w = pack_f16x2(__uint_as_float(cur[i * 8 + 6]) * inv_l, __uint_as_float(cur[i * 8 + 7]) * inv_l);
+            const int unit = ((c & 3) * 2 + i) ^ (lane & 7);
+            *reinterpret_cast<uint4*>(prow + unit * 16) = v;
           }
         }
+        fence_proxy_async_smem();
         // O of this stage has been read: let the next item's first product overwrite it
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&p_full[s]);
+        if (lane == 0) {
+          const int row0 = g.r0[s] + static_cast<int>(lane_base);
+          if (row0 < N) {  // rows of the box beyond the sequence are clipped by the store
+            tma_store_4d(&mapO, out_stage, 0, row0, 0, g.bh);
+            tma_store_commit();
+          }
+          mbar_arrive(&p_full[s]);
+        }
         arrived_early[s] = true;
       };
       for (int j = g.lo_all; j < g.hi_all && ok; ++j) {
@@ -520,6 +539,7 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       if (epi_pending[0]) epilogue(std::integral_constant<int, 0>{});
       if (ok && epi_pending[1]) epilogue(std::integral_constant<int, 1>{});
     }
+    if (lane == 0) tma_store_wait_all();  // also on the give-up path: stores in flight read this CTA's shared memory
   } else {
     reg_dec<FA_REG_MISC>();
     if (warp == 12) {
