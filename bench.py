@@ -43,9 +43,9 @@ OTHER_CONFIGS = [
 # traffic per head carries over to the full workload only while heads are scheduled in groups of the same size there
 # (checked at run time: TRAFFIC_HEAD_GROUP).
 TRAFFIC_CASE = dict(name="C5s", B=1, H=12, N=32768, d=128, causal=True, wl=-1, wr=-1)
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of TRAFFIC_CASE under ncu (442.9 MB + 88.3 MB for 12
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of TRAFFIC_CASE under ncu (456.3 MB + 84.8 MB for 12
 # heads), per head. Algorithmic bytes per head are 33.6 MB.
-TRAFFIC_BYTES_PER_HEAD = (442907648 + 88302336) / 12
+TRAFFIC_BYTES_PER_HEAD = (456277504 + 84791040) / 12
 TRAFFIC_HEAD_GROUP = 4  # heads per scheduling group during that capture
 METRIC = "fwd attention TFLOP/s (whole job; FLOPs = 4*B*H*N^2*d, halved for causal)"
 FALLBACK_TFLOPS = 1590.0  # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
