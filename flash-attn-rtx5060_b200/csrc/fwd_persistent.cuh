@@ -412,6 +412,10 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         else tile_body(std::false_type{});
       }
       if (!ok) break;
+      // The row sums of the previous item may still be unread when this item is a single tile. The last tile's
+      // p_full phase completes only after the correction warps have arrived on it, and on an item's first tile
+      // they do that after their epilogue of the previous item, which reads the sums first.
+      if (!mbar_wait_warp(&p_full[s], (n_s - 1) & 1, abort_flag)) break;
       sRowSum[s * kBlockM + row_l] = l_run;
       __syncwarp();
       if (lane == 0) mbar_arrive(&l_ready[s]);
