@@ -228,6 +228,12 @@ def main():
                     "(head_dim 128 cases)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    # stdout carries the JSON line and nothing else: whatever a library prints there on its own (NCCL's version
+    # banner, for one) is sent to stderr by pointing descriptor 1 at it; the line is written to the saved descriptor.
+    sys.stdout.flush()
+    real_stdout = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    sys.stdout = real_stdout
     if args.impl == "reference":
         return run_reference(args)
 
@@ -241,8 +247,6 @@ def main():
     torch.cuda.set_device(local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # NCCL's own log lines (its version banner, for one) go to stderr: stdout carries the one JSON line
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     pkg = entry.load_package()
     pkg.lib()  # fails loudly if the CUDA library is missing
