@@ -429,6 +429,9 @@ static int forward_impl(const void* q, const void* k, const void* v, void* o, in
   if (kernel < 0 || kernel > 2) return fail(FA_INVALID_ARG, "kernel must be 0 (default), 1 (serial) or 2 (CTA pair)");
   if (kernel == 2 && head_dim != 128) return fail(FA_UNSUPPORTED, "the CTA-pair kernel needs head_dim 128");
   if (!(softmax_scale == softmax_scale)) return fail(FA_INVALID_ARG, "softmax_scale is NaN");
+  // (hidden scores are pushed to about -3e38 before the scale is applied: a scale this small would bring them back)
+  if (softmax_scale > 3.0e38f || (softmax_scale > 0.f && softmax_scale < 1.0e-30f))
+    return fail(FA_INVALID_ARG, "softmax_scale must be a finite value of at least 1e-30 (or <= 0 for 1/sqrt(head_dim))");
   if (!(dropout_prob >= 0.f && dropout_prob <= 1.f)) return fail(FA_INVALID_ARG, "dropout_prob must lie in [0, 1]");
   // keep threshold in 1/256 steps (nearest); a probability below 1/512 keeps everything and takes the plain kernel
   const unsigned keep_thr = (unsigned)rintf(256.f * (1.f - dropout_prob));
@@ -694,6 +697,9 @@ int flash_forward_noalloc(const void* q, const void* k, const void* v, void* o, 
     return FA_INVALID_ARG;
   }
   if (!(softmax_scale == softmax_scale)) return fail(FA_INVALID_ARG, "softmax_scale is NaN");
+  // (hidden scores are pushed to about -3e38 before the scale is applied: a scale this small would bring them back)
+  if (softmax_scale > 3.0e38f || (softmax_scale > 0.f && softmax_scale < 1.0e-30f))
+    return fail(FA_INVALID_ARG, "softmax_scale must be a finite value of at least 1e-30 (or <= 0 for 1/sqrt(head_dim))");
   const long long bh_ll = (long long)batch * heads;
   const int pairs = (seqlen + 2 * fa::kBlockM - 1) / (2 * fa::kBlockM);
   // the work counter in the scratch is a 32-bit int to which the kernel adds the grid size

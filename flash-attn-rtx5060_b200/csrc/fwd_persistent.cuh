@@ -340,12 +340,23 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
               sc[c] = fmaf(sc[c], p.scale_log2, -slope_l2 * fabsf(rel - static_cast<float>(c)));
           }
           if (kMasked) {
-            const int c_lo = (wl >= 0) ? row - wl - kv0 : -1;
+            // Visible columns of this row: c_lo <= c <= c_hi, i.e. |c - mid| <= half. The predicate is applied on the
+            // FMA pipe, which the softmax leaves nearly idle, instead of as two integer compares and a select per
+            // element: t = saturate(|c - mid| - half) is 0 for a visible column and 1 for a hidden one (both
+            // operands are multiples of 1/2, so the difference is exact), and sc - kHidden * t leaves a visible
+            // score bit for bit as it is and puts a hidden one near -3e38, where its exponential is 0 for any scale the
+            // host accepts.
+            const int c_lo = (wl >= 0) ? row - wl - kv0 : -(1 << 20);
             int c_hi = N - 1 - kv0;
             if (wr >= 0) c_hi = min(c_hi, row + wr - kv0);
+            const float mid = 0.5f * static_cast<float>(c_lo + c_hi);
+            const float half = 0.5f * static_cast<float>(c_hi - c_lo);  // negative: no visible column at all
+            constexpr float kHidden = 3.0e38f;
   #pragma unroll
-            for (int c = 0; c < kBlockN; ++c)
-              if (c < c_lo || c > c_hi) sc[c] = -INFINITY;
+            for (int c = 0; c < kBlockN; ++c) {
+              const float t = __saturatef(fabsf(static_cast<float>(c) - mid) - half);
+              sc[c] = fmaf(t, -kHidden, sc[c]);
+            }
           }
           // The exponentials of the first 32 keys are taken against the reference the previous tile left while
           // the row max of this tile is still being reduced: nearly always the reference stays where it is (lazy
@@ -365,7 +376,8 @@ fwd_persistent_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             mx2 = max3(mx2, sc[c + 4], sc[c + 5]);
             mx3 = max3(mx3, sc[c + 6], sc[c + 7]);
           }
-          const float m_new = max3(mx0, mx1, fmaxf(mx2, mx3));
+          float m_new = max3(mx0, mx1, fmaxf(mx2, mx3));
+          if (kMasked && m_new < -1.0e37f) m_new = -INFINITY;  // nothing visible so far (hidden scores sit near -3e38)
           // The reference moves when the true max has grown past it by more than kLazyLog2 (P then stays below
           // 2^8, well inside fp16), and always on the first tile that shows a finite score: the reference then IS
           // the row max, so the largest term of the row is exactly 1 in fp16 (a row with a single visible key

@@ -32,7 +32,8 @@ enum {
  * with the argument list the reference's call site uses (src/main.cu:99) reduced to what the
  * path reads: Q/K/V/O, batch, heads, seqlen, head_dim, softmax scale, causal flag, window.
  *
- *   softmax_scale <= 0  -> 1/sqrt(head_dim)  (what the reference hard-codes, :639)
+ *   softmax_scale <= 0  -> 1/sqrt(head_dim)  (what the reference hard-codes, :639); a positive scale has to be
+ *                          finite and at least 1e-30 (FA_INVALID_ARG otherwise)
  *   is_causal != 0      -> key j visible to query i only if j <= i
  *   window_left  >= 0   -> key j visible only if j >= i - window_left   (< 0: unbounded)
  *   window_right >= 0   -> key j visible only if j <= i + window_right  (< 0: unbounded)

@@ -49,6 +49,10 @@ def test_argument_errors_are_status_codes(pkg):
     assert b"head_dim" in L.flash_forward_last_error()
     assert L.flash_forward(ctypes.c_void_p(0x1008), p, p, p, 1, 1, 128, 64, 0.0, 0, -1, -1, None) == pkg.FA_INVALID_ARG
     assert L.flash_forward_ex(p, p, p, p, 1, 1, 128, 64, 0.0, 0, -1, -1, None, 7, 0, None) == pkg.FA_INVALID_ARG
+    # a softmax scale that is not finite, or so small that masked scores would come back into range
+    for bad in (float("nan"), float("inf"), 1e-35):
+        assert L.flash_forward(p, p, p, p, 1, 1, 128, 64, bad, 0, -1, -1, None) == pkg.FA_INVALID_ARG
+        assert b"softmax_scale" in L.flash_forward_last_error()
     # dropout probability outside [0, 1]
     assert L.run_flash_attention_c(1, 1, 128, 64, p, p, p, p, None, None, 1, 0, 0, 0, 0, None, 1.5, None) == pkg.FA_INVALID_ARG
     assert L.flash_forward_dropout(p, p, p, p, 1, 1, 128, 64, 0.0, 0, -1, -1, None, -0.5, 0, None) == pkg.FA_INVALID_ARG
