@@ -342,6 +342,22 @@ def test_explicit_scale_and_large_logits(pkg, ob):
         assert_close(ob, got, want, max_abs=5e-2, mean_abs=1e-3)
 
 
+@pytest.mark.parametrize("scale", [1e-20, 1e-6])
+def test_tiny_scale_keeps_hidden_keys_hidden(pkg, ob, scale):
+    # The kernel hides a masked score by pushing it to about -3e38 BEFORE the scale is applied. With a scale near the
+    # smallest the host accepts every visible key gets the same weight, so row i of a causal, left-windowed call is
+    # the plain mean of V over its visible keys; a hidden key that leaked back in would show as a wrong mean.
+    N, d, wl = 700, 64, 200
+    q, k, v = make_inputs(17, 1, 2, N, d)
+    got = run_gpu(pkg, q, k, v, True, wl, -1, 0, scale=scale).astype(np.float64)
+    v64 = v.astype(np.float64)
+    csum = np.concatenate([np.zeros((1, 2, 1, d)), np.cumsum(v64, axis=2)], axis=2)
+    for i in (0, 1, 127, 128, 199, 200, 201, 333, 511, 512, 699):
+        lo = max(0, i - wl)
+        want = (csum[:, :, i + 1] - csum[:, :, lo]) / (i + 1 - lo)
+        assert np.abs(got[:, :, i] - want).max() <= 2e-3, i
+
+
 def test_growing_row_max_forces_rescale(pkg, ob):
     # keys ordered so that every later kv tile raises the row max by far more than the lazy threshold
     N, d = 1024, 64
