@@ -5,7 +5,7 @@
 //   warps 0-3   softmax of q tile 0: one thread per score row (TMEM lane), exp2 online softmax
 //   warps 4-7   softmax of q tile 1
 //   warps 8-11  correction: rescales the running output in TMEM when a row max moved, and the
-//               epilogue (O / l -> fp16 -> global)
+//               epilogue (O / l -> fp16 -> the warp's staging area in shared memory -> one TMA store)
 //   warp 12     tensor-core issuer: the warp walks the schedule, one elected lane issues tcgen05.mma
 //   warp 13     TMA producer: Q tiles and the K/V tile ring
 //   warps 14-15 idle (they only donate registers)
