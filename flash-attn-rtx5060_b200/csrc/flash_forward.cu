@@ -78,8 +78,15 @@ struct DeviceState {
 // Hands out the scheduler words for one launch on `st`. Call with s->mu held; `*slot_out` is passed to
 // sched_release() right after the launch, under the same lock.
 int sched_acquire(DeviceState* s, cudaStream_t st, int** words, int* slot_out) {
-  const int slot = (int)(s->next_sched++ % kSchedSlots);
   cudaError_t e;
+  // A captured launch would keep its pair of words for every replay, while the pairs are handed out in turn to
+  // later launches: two kernels could then share one work counter. The entry point with a caller-chosen slot
+  // (flash_forward_noalloc) is the one to capture.
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if ((e = cudaStreamIsCapturing(st, &cap)) != cudaSuccess) return fail_cuda("cudaStreamIsCapturing", e);
+  if (cap != cudaStreamCaptureStatusNone)
+    return fail(FA_UNSUPPORTED, "this entry point cannot be captured into a CUDA graph; capture flash_forward_noalloc");
+  const int slot = (int)(s->next_sched++ % kSchedSlots);
   if (!s->slot_done[slot] &&
       (e = cudaEventCreateWithFlags(&s->slot_done[slot], cudaEventDisableTiming)) != cudaSuccess)
     return fail_cuda("cudaEventCreate(scheduler slot)", e);

@@ -49,8 +49,9 @@ enum {
  * few hundred bytes, allocated on the first call per device) in turn. Launches on one stream are
  * ordered anyway; when a pair is reused by a launch on ANOTHER stream, that stream is first made to
  * wait (cudaStreamWaitEvent) for the earlier launch, so any number of launches may be queued on any
- * number of streams. Because of that event the call must not be made while its stream is being
- * captured into a CUDA graph: a captured launch would keep its pair for every replay.
+ * number of streams. A call whose stream is being captured into a CUDA graph is refused with
+ * FA_UNSUPPORTED: a captured launch would keep its pair for every replay. flash_forward_noalloc, whose
+ * scratch slot the caller chooses, is the entry point to capture.
  */
 int flash_forward(const void* q, const void* k, const void* v, void* o, int batch, int heads, int seqlen,
                   int head_dim, float softmax_scale, int is_causal, int window_left, int window_right,

@@ -62,6 +62,50 @@ def test_noalloc_async_then_other_slot(pkg, ob):
     assert nans == 0 and mx <= 2e-3 and mean <= 2e-4
 
 
+def test_noalloc_in_a_cuda_graph_and_the_allocating_entry_point_refuses_capture(pkg, ob):
+    # The entry point with a caller-chosen scratch slot is the one to capture: two launches (two slots) go into one
+    # graph, the graph is replayed on new inputs in the same buffers, and every replay equals the eager result.
+    # flash_forward itself answers FA_UNSUPPORTED while its stream is being captured, and leaves the capture intact.
+    import torch
+
+    B, H, N, d = 1, 6, 640, 128
+    q, k, v = make_inputs(47, B, H, N, d)
+    tq, tk, tv = (torch.from_numpy(a).cuda() for a in (q, k, v))
+    o1, o2 = torch.empty_like(tq), torch.empty_like(tq)
+    assert call_noalloc(pkg, tq, tk, tv, o1, B, H, N, d, True, -1, -1, slot=4) == pkg.FA_OK  # first call: no capture yet
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            st = torch.cuda.current_stream().cuda_stream
+            L = pkg.lib()
+            rc_plain = L.flash_forward(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), o1.data_ptr(), B, H, N, d, 0.0, 1,
+                                       -1, -1, st)
+            rc1 = L.flash_forward_noalloc(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), o1.data_ptr(), B, H, N, d, 0.0,
+                                          1, -1, -1, st, 4, 0)
+            rc2 = L.flash_forward_noalloc(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), o2.data_ptr(), B, H, N, d, 0.0,
+                                          0, 100, 50, st, 5, 0)
+    assert rc_plain == pkg.FA_UNSUPPORTED and b"graph" in pkg.lib().flash_forward_last_error()
+    assert rc1 == pkg.FA_OK and rc2 == pkg.FA_OK
+    for seed in (48, 49, 50):
+        q, k, v = make_inputs(seed, B, H, N, d)
+        for t, a in ((tq, q), (tk, k), (tv, v)):
+            t.copy_(torch.from_numpy(a))
+        o1.fill_(float("nan"))
+        o2.fill_(float("nan"))
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert pkg.lib().flash_forward_noalloc_check(None, 4) == pkg.FA_OK
+        assert pkg.lib().flash_forward_noalloc_check(None, 5) == pkg.FA_OK
+        want1 = pkg.attention_forward(tq, tk, tv, causal=True)
+        want2 = pkg.attention_forward(tq, tk, tv, causal=False, window_left=100, window_right=50)
+        torch.cuda.synchronize()
+        assert torch.equal(o1, want1) and torch.equal(o2, want2), seed
+    mx, mean, nans = ob.abs_error(o1.cpu().numpy(), ob.attention(q, k, v, causal=True))
+    assert nans == 0 and mx <= 2e-3 and mean <= 2e-4
+
+
 def test_noalloc_rejects_what_the_scratch_cannot_hold(pkg):
     import torch
 
